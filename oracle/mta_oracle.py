@@ -1,0 +1,151 @@
+"""ctypes/numpy front end of the C oracle in mta_oracle.c.  TEST INFRASTRUCTURE ONLY.
+
+Only the test-suite, the smoke check and the benchmark's CPU-baseline leg may import this
+module; the product package never does.  Every function takes and returns float32 numpy arrays
+(values already rounded to the run dtype by the caller) and mirrors one entry of the C file, which
+cites the reference lines it restates.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from typing import Optional
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libmta_oracle.so")
+_lib: Optional[ctypes.CDLL] = None
+
+ROUND_NONE, ROUND_BF16, ROUND_FP16 = 0, 1, 2
+
+
+def build(force: bool = False) -> str:
+    """Compile mta_oracle.c with gcc (via the Makefile beside it) and return the .so path."""
+    src = os.path.join(_HERE, "mta_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "-B", "libmta_oracle.so"])
+    return _SO
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(_SO)
+        fp = ctypes.POINTER(ctypes.c_float)
+        i = ctypes.c_int
+        L.mta_oracle_conv2d.argtypes = [fp, fp, fp, i, i, i, i, i, i, i, i]
+        L.mta_oracle_head_linear.argtypes = [fp, fp, fp, i, i, i, i, i, ctypes.c_float, i]
+        L.mta_oracle_softmax.argtypes = [fp, fp, ctypes.c_long, i, i, i, i]
+        L.mta_oracle_round.argtypes = [fp, fp, ctypes.c_long, i]
+        L.mta_oracle_mta_fwd_rows.argtypes = [fp] * 7 + [i] * 13 + [fp]
+        L.mta_oracle_conv_attn_fwd_rows.argtypes = [fp] * 4 + [i] * 7 + [ctypes.c_float] + [i] * 4 + [fp]
+        L.mta_oracle_set_threads.argtypes = [i]
+        for name in ("mta_oracle_conv2d", "mta_oracle_head_linear", "mta_oracle_softmax",
+                     "mta_oracle_mta_fwd_rows", "mta_oracle_conv_attn_fwd_rows",
+                     "mta_oracle_num_threads", "mta_oracle_abi_version"):
+            getattr(L, name).restype = i
+        _lib = L
+    return _lib
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"oracle {what} failed with status {rc}")
+
+
+def num_threads() -> int:
+    return lib().mta_oracle_num_threads()
+
+
+def set_threads(n: int) -> None:
+    lib().mta_oracle_set_threads(int(n))
+
+
+def round_to(a, mode: int) -> np.ndarray:
+    a = _f32(a)
+    out = np.empty_like(a)
+    lib().mta_oracle_round(_p(a), _p(out), a.size, mode)
+    return out
+
+
+def conv2d(x, w, causal: bool, round_mode: int = ROUND_NONE) -> np.ndarray:
+    """Depthwise causal conv on (N,C,H,W) with weight (C,R,S)."""
+    x, w = _f32(x), _f32(w)
+    N, C, H, W = x.shape
+    Cw, R, S = w.shape
+    assert Cw == C
+    y = np.empty_like(x)
+    _check(lib().mta_oracle_conv2d(_p(x), _p(w), _p(y), N, C, H, W, R, S, int(causal), round_mode), "conv2d")
+    return y
+
+
+def head_linear(x, Wm, causal: bool = True, fill: float = 0.0, round_mode: int = ROUND_NONE) -> np.ndarray:
+    """Head-mixing linear on (N,C,P,Q) with weight (C,C) in nn.Linear orientation."""
+    x, Wm = _f32(x), _f32(Wm)
+    N, C, P, Q = x.shape
+    assert Wm.shape == (C, C)
+    y = np.empty_like(x)
+    _check(lib().mta_oracle_head_linear(_p(x), _p(Wm), _p(y), N, C, P, Q, int(causal), float(fill), round_mode),
+           "head_linear")
+    return y
+
+
+def softmax(x, causal: bool = True, round_mode: int = ROUND_NONE) -> np.ndarray:
+    x = _f32(x)
+    P, Q = x.shape[-2], x.shape[-1]
+    y = np.empty_like(x)
+    _check(lib().mta_oracle_softmax(_p(x), _p(y), x.size // Q, P, Q, int(causal), round_mode), "softmax")
+    return y
+
+
+def mta_fwd_rows(q, k, v, w1, W1, w2, W2, b: int, r0: int, r1: int, causal: bool = True,
+                 round_mode: int = ROUND_NONE) -> np.ndarray:
+    """Full MTA forward for batch element b, rows [r0,r1): returns (H, r1-r0, D)."""
+    q, k, v, w1, W1, w2, W2 = map(_f32, (q, k, v, w1, W1, w2, W2))
+    B, H, S, D = q.shape
+    _, cq, ck = w1.shape
+    _, cq2, ck2 = w2.shape
+    out = np.empty((H, r1 - r0, D), dtype=np.float32)
+    _check(lib().mta_oracle_mta_fwd_rows(_p(q), _p(k), _p(v), _p(w1), _p(W1), _p(w2), _p(W2), B, H, S, D,
+                                         cq, ck, cq2, ck2, int(causal), round_mode, b, r0, r1, _p(out)),
+           "mta_fwd_rows")
+    return out
+
+
+def mta_fwd(q, k, v, w1, W1, w2, W2, causal: bool = True, round_mode: int = ROUND_NONE) -> np.ndarray:
+    """Full MTA forward: returns (B,H,S,D) (the reference returns its (B,S,H,D) transpose view)."""
+    q = _f32(q)
+    B, H, S, D = q.shape
+    return np.stack([mta_fwd_rows(q, k, v, w1, W1, w2, W2, b, 0, S, causal, round_mode) for b in range(B)])
+
+
+def conv_attn_fwd_rows(q, k, v, w, b: int, r0: int, r1: int, causal: bool = True,
+                       softmax_scale: Optional[float] = None, round_mode: int = ROUND_NONE) -> np.ndarray:
+    q, k, v, w = map(_f32, (q, k, v, w))
+    B, H, S, D = q.shape
+    _, cq, ck = w.shape
+    if softmax_scale is None:
+        softmax_scale = 1.0 / (D ** 0.5)
+    out = np.empty((H, r1 - r0, D), dtype=np.float32)
+    _check(lib().mta_oracle_conv_attn_fwd_rows(_p(q), _p(k), _p(v), _p(w), B, H, S, D, cq, ck, int(causal),
+                                               float(softmax_scale), round_mode, b, r0, r1, _p(out)),
+           "conv_attn_fwd_rows")
+    return out
+
+
+def conv_attn_fwd(q, k, v, w, causal: bool = True, softmax_scale: Optional[float] = None,
+                  round_mode: int = ROUND_NONE) -> np.ndarray:
+    q = _f32(q)
+    B, H, S, D = q.shape
+    return np.stack([conv_attn_fwd_rows(q, k, v, w, b, 0, S, causal, softmax_scale, round_mode) for b in range(B)])
