@@ -1,0 +1,121 @@
+/*
+ * mta_b200 — C ABI of the B200 (sm_100a) Multi-Token-Attention forward library.
+ *
+ * Every pointer named x, w, y, q, k, v, o, workspace is a DEVICE pointer owned by the caller.
+ * Unless a function says otherwise nothing here allocates or frees memory, every launch is
+ * asynchronous on the cudaStream_t passed as `stream` (a void* so that this header needs no CUDA
+ * include), and the return value is a status code:
+ *     0 ok, 1 invalid argument / unsupported shape, 2 CUDA runtime error, 3 device is not sm_100,
+ *     4 a device-side bounded wait ran out.
+ * After a non-zero return mta_last_error() gives a thread-local, human-readable reason.
+ * The functions never throw and never abort the process.
+ *
+ * dtype codes: 0 float32, 1 bfloat16, 2 float16.  Weights may be float32 or the activation dtype.
+ *
+ * Each entry point names the interface of the reference project that it stands in for
+ * (paths relative to that project).
+ */
+#ifndef MTA_B200_H
+#define MTA_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MTA_OK = 0, MTA_ERR_INVALID = 1, MTA_ERR_CUDA = 2, MTA_ERR_ARCH = 3, MTA_ERR_TIMEOUT = 4 };
+enum { MTA_F32 = 0, MTA_BF16 = 1, MTA_F16 = 2 };
+
+/* Version of this ABI; bumped on any signature change. */
+int mta_abi_version(void);
+
+/* Thread-local description of the last failure on the calling thread ("" if none). */
+const char* mta_last_error(void);
+
+/*
+ * Depthwise causal 2-D convolution over a score plane.
+ * Replaces Conv2dTritonFunction.forward + conv_fwd_kernel (convolution_2d_trit.py:301-333, :52-135).
+ *   x, y: (N,C,H,W) contiguous, dtype x_dtype.  w: (C,R,S), dtype w_dtype.
+ *   y[n,c,q,k] = sum_{i<R,j<S} w[c,i,j] * xh[n,c,q+i-(R-1),k+j-(S-1)/2], fp32 accumulation;
+ *   xh is x inside the plane and 0 outside; when causal, xh is 0 where k' > q' (input above the
+ *   diagonal is never read) and y is written as 0 where k > q.  The whole of y is written.
+ */
+int mta_conv2d_fwd(const void* x, const void* w, void* y, int N, int C, int H, int W, int R, int S,
+                   int causal, int x_dtype, int w_dtype, void* stream);
+
+/*
+ * Head-mixing linear across the channel (head) axis of a score plane, without a transpose.
+ * Replaces TritonLinearHeadFunction.forward + linear_head_kernel_forward
+ * (triton_linear_head.py:283-319, :76-139).
+ *   x, y: (N,C,P,Q) contiguous.  Wm: (C,C) in nn.Linear orientation: y[n,o,p,q] = sum_h Wm[o,h] x[n,h,p,q]
+ *   for q <= p (everywhere if not causal); y = fill where q > p (the reference pre-fills the output
+ *   with `output_value`, :294-297).  fill may be -inf.  The whole of y is written.
+ */
+int mta_head_linear_fwd(const void* x, const void* Wm, void* y, int N, int C, int P, int Q, int causal,
+                        float fill, int x_dtype, int w_dtype, void* stream);
+
+/*
+ * Row softmax over keys q <= p (causal) or all keys, computed in fp32, output in the input dtype;
+ * entries above the diagonal are written as 0.  Stands in for the F.softmax(scores.float(), -1)
+ * .type_as(xq) step of MTAAttentionTriton.forward (mta_attention_triton.py:79) reading only the
+ * lower triangle.  x, y: (N,C,P,Q) contiguous; x may equal y.
+ */
+int mta_softmax_fwd(const void* x, void* y, int N, int C, int P, int Q, int causal, int dtype, void* stream);
+
+/*
+ * Scaled scores Q K^T * scale for keys k <= q (entries above the diagonal are left untouched when
+ * causal) and P V over keys k <= q.  They stand in for the two torch.matmul calls of
+ * MTAAttentionTriton.forward (mta_attention_triton.py:68-71, :89).  q,k,v,o: (B,H,S,D); s,p: (B,H,S,S).
+ * `round_scale` != 0 reproduces the reference's 16-bit rounding (matmul result rounded, then
+ * multiplied by the rounded scale and rounded again).
+ */
+int mta_qk_scores_fwd(const void* q, const void* k, void* s, int B, int H, int S, int D, float scale,
+                      int round_scale, int causal, int dtype, void* stream);
+int mta_pv_fwd(const void* p, const void* v, void* o, int B, int H, int S, int D, int causal, int dtype,
+               void* stream);
+
+/*
+ * Fused conv attention forward: softmax(scale * conv(Q K^T)) V with the causal conv of
+ * mta_conv2d_fwd applied to the unscaled scores.
+ * Replaces TritonAttention.forward + _attn_fwd (conv_attention_triton.py:362-452, :167-356);
+ * oracle ConvAttention.forward (conv_attention_pytorch.py:36-91).
+ *   q,k,v,o: (B,H,S,D) contiguous; w: (H,cq,ck).  Needs mta_conv_attn_workspace_bytes(...) bytes of
+ *   caller-provided scratch (contents undefined on entry and exit).
+ */
+size_t mta_conv_attn_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int dtype);
+int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w, void* o, void* workspace,
+                      size_t workspace_bytes, int B, int H, int S, int D, int cq, int ck, int causal,
+                      float scale, int dtype, int w_dtype, void* stream);
+
+/*
+ * Full four-stage MTA forward: QK^T/sqrt(D) -> conv (w1) -> head mix (W1) -> softmax -> conv (w2) ->
+ * head mix (W2) -> @V, for batch elements [0,B) and query rows [q_row_begin, q_row_end).
+ * Replaces the body of MTAAttentionTriton.forward (mta_attention_triton.py:61-92) with use_mask=False;
+ * oracle MTAAttention.forward (mta_attention_pytorch.py:58-83).
+ *   q,k,v,o: (B,H,S,D) contiguous (the Python module returns o.transpose(1,2) as the reference does);
+ *   only rows [q_row_begin,q_row_end) of o are written.  w1 (H,cq,ck), W1 (H,H), w2 (H,cq2,ck2), W2 (H,H).
+ *   ck and ck2 must be odd.  Needs mta_workspace_bytes(...) bytes of scratch.
+ * The row range is what a caller sharding query rows over several GPUs passes: rows before
+ * q_row_begin that the two convs reach back to ((cq-1)+(cq2-1) of them) are recomputed internally.
+ */
+size_t mta_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int cq2, int ck2, int q_row_begin,
+                           int q_row_end, int dtype);
+int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, const void* W1, const void* w2,
+                  const void* W2, void* o, void* workspace, size_t workspace_bytes, int B, int H, int S, int D,
+                  int cq, int ck, int cq2, int ck2, int q_row_begin, int q_row_end, int causal, int dtype,
+                  int w_dtype, void* stream);
+
+/* Number of kernel launches issued by this library on the calling thread since the last reset
+ * (what a benchmark reports as its launch count). */
+long mta_launch_count(void);
+void mta_reset_launch_count(void);
+
+/* Selects implementation variants for A/B measurement: key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core;
+ * key "conv2d" -> 0 auto, 1 CUDA-core, 2 tensor-core.  Returns 0, or 1 for an unknown key/value. */
+int mta_set_variant(const char* key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MTA_B200_H */

@@ -1,0 +1,134 @@
+// C ABI of the library: argument validation, error text, and dispatch to the kernel launchers.
+// See include/mta_b200.h for the contract of every entry point.
+#include <cstring>
+#include <string>
+
+#include "kernels.cuh"
+
+namespace mta {
+namespace {
+thread_local char g_error[512] = "";
+thread_local long g_launches = 0;
+int g_variant_head_linear = 0;
+int g_variant_conv2d = 0;
+int g_variant_gemm = 0;
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+void count_launch(int n) { g_launches += n; }
+
+int variant(const char* key) {
+    if (!strcmp(key, "head_linear")) return g_variant_head_linear;
+    if (!strcmp(key, "conv2d")) return g_variant_conv2d;
+    if (!strcmp(key, "gemm")) return g_variant_gemm;
+    return 0;
+}
+
+int check_device() {
+    int dev = 0;
+    MTA_CUDA_OK(cudaGetDevice(&dev));
+    int major = 0;
+    MTA_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) {
+        set_error("device %d has compute capability %d.x; this library is built for sm_100a only", dev, major);
+        return MTA_ERR_ARCH;
+    }
+    return MTA_OK;
+}
+
+PlaneView full_view(int rows, int cols) { return PlaneView{(long)rows * cols, 0, cols}; }
+
+}  // namespace mta
+
+using namespace mta;
+
+extern "C" {
+
+int mta_abi_version(void) { return 1; }
+
+const char* mta_last_error(void) { return g_error; }
+
+long mta_launch_count(void) { return g_launches; }
+void mta_reset_launch_count(void) { g_launches = 0; }
+
+int mta_set_variant(const char* key, int value) {
+    if (!key || value < 0 || value > 2) return MTA_ERR_INVALID;
+    if (!strcmp(key, "head_linear")) g_variant_head_linear = value;
+    else if (!strcmp(key, "conv2d")) g_variant_conv2d = value;
+    else if (!strcmp(key, "gemm")) g_variant_gemm = value;
+    else return MTA_ERR_INVALID;
+    return MTA_OK;
+}
+
+int mta_conv2d_fwd(const void* x, const void* w, void* y, int N, int C, int H, int W, int R, int S, int causal,
+                   int x_dtype, int w_dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(x_dtype) && dtype_ok(w_dtype), "conv2d: unknown dtype code (x %d, w %d)", x_dtype, w_dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && H >= 0 && W >= 0, "conv2d: bad shape N=%d C=%d H=%d W=%d", N, C, H, W);
+    MTA_REQUIRE(R >= 1 && S >= 1, "conv2d: kernel size %dx%d must be positive", R, S);
+    if ((long)N * H * W == 0) return MTA_OK;
+    MTA_REQUIRE(x && w && y, "conv2d: null pointer");
+    MTA_REQUIRE(x != y, "conv2d: in-place operation is not supported");
+    if (int rc = check_device()) return rc;
+    const PlaneView v = full_view(H, W);
+    return conv2d_launch(x, v, w, w_dtype, y, v, (long)N * C, C, H, W, R, S, causal ? 1 : 0, 0, H, true, x_dtype,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int mta_head_linear_fwd(const void* x, const void* Wm, void* y, int N, int C, int P, int Q, int causal, float fill,
+                        int x_dtype, int w_dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(x_dtype) && dtype_ok(w_dtype), "head_linear: unknown dtype code (x %d, w %d)", x_dtype, w_dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && P >= 0 && Q >= 0, "head_linear: bad shape N=%d C=%d P=%d Q=%d", N, C, P, Q);
+    if ((long)N * P * Q == 0) return MTA_OK;
+    MTA_REQUIRE(x && Wm && y, "head_linear: null pointer");
+    MTA_REQUIRE(x != y, "head_linear: in-place operation is not supported");
+    if (int rc = check_device()) return rc;
+    const PlaneView v = full_view(P, Q);
+    return head_linear_launch(x, v, Wm, w_dtype, y, v, N, C, P, Q, causal ? 1 : 0, fill, 0, P, true, x_dtype,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int mta_softmax_fwd(const void* x, void* y, int N, int C, int P, int Q, int causal, int dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(dtype), "softmax: unknown dtype code %d", dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && P >= 0 && Q >= 0, "softmax: bad shape N=%d C=%d P=%d Q=%d", N, C, P, Q);
+    if ((long)N * P * Q == 0) return MTA_OK;
+    MTA_REQUIRE(x && y, "softmax: null pointer");
+    if (int rc = check_device()) return rc;
+    const PlaneView v = full_view(P, Q);
+    return softmax_launch(x, v, y, v, (long)N * C, P, Q, causal ? 1 : 0, 0, P, true, 1.0f, dtype,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int mta_qk_scores_fwd(const void* q, const void* k, void* s, int B, int H, int S, int D, float scale, int round_scale,
+                      int causal, int dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(dtype), "qk_scores: unknown dtype code %d", dtype);
+    MTA_REQUIRE(B >= 0 && H >= 1 && S >= 0 && D >= 1, "qk_scores: bad shape B=%d H=%d S=%d D=%d", B, H, S, D);
+    if ((long)B * S == 0) return MTA_OK;
+    MTA_REQUIRE(q && k && s, "qk_scores: null pointer");
+    MTA_REQUIRE((long)B * H <= 65535, "qk_scores: B*H = %ld exceeds 65535", (long)B * H);
+    if (int rc = check_device()) return rc;
+    return qk_scores_launch(q, k, s, full_view(S, S), B, H, S, D, scale, round_scale, causal ? 1 : 0, 0, S, dtype,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int mta_pv_fwd(const void* p, const void* v, void* o, int B, int H, int S, int D, int causal, int dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(dtype), "pv: unknown dtype code %d", dtype);
+    MTA_REQUIRE(B >= 0 && H >= 1 && S >= 0 && D >= 1, "pv: bad shape B=%d H=%d S=%d D=%d", B, H, S, D);
+    if ((long)B * S == 0) return MTA_OK;
+    MTA_REQUIRE(p && v && o, "pv: null pointer");
+    MTA_REQUIRE((long)B * H <= 65535, "pv: B*H = %ld exceeds 65535", (long)B * H);
+    if (int rc = check_device()) return rc;
+    return pv_launch(p, full_view(S, S), v, o, B, H, S, D, causal ? 1 : 0, 0, S, dtype, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,118 @@
+// The two composite forwards of the C ABI.
+//
+//   mta_fused_fwd      QK^T/sqrt(D) -> conv(w1) -> head mix(W1) -> softmax -> conv(w2) -> head mix(W2) -> @V
+//                      (body of MTAAttentionTriton.forward, mta_attention_triton.py:61-92, use_mask=False)
+//   mta_conv_attn_fwd  softmax(scale * conv(Q K^T)) V   (TritonAttention.forward, conv_attention_triton.py:362-452)
+//
+// Both keep two score-plane scratch buffers in the caller's workspace, indexed by absolute query row
+// relative to the first row the request needs, so a query-row range [q_row_begin, q_row_end) costs
+// memory and work proportional to that range (plus the rows the convs reach back to).  Nothing above
+// the diagonal of a scratch plane is ever written or read.
+#include "kernels.cuh"
+
+namespace mta {
+namespace {
+
+struct Plan {
+    int ra, rb, r0, r1;      // first score row, first softmax row, first and one-past-last output row
+    size_t buf_bytes;        // one scratch buffer
+};
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+Plan make_plan(int B, int H, int S, int cq, int cq2, int r0, int r1, int dtype) {
+    Plan p;
+    p.r0 = r0;
+    p.r1 = r1;
+    p.rb = r0 - (cq2 - 1) > 0 ? r0 - (cq2 - 1) : 0;
+    p.ra = p.rb - (cq - 1) > 0 ? p.rb - (cq - 1) : 0;
+    p.buf_bytes = round_up((size_t)B * H * (size_t)(r1 - p.ra) * S * dtype_size(dtype), 256);
+    return p;
+}
+
+}  // namespace
+}  // namespace mta
+
+using namespace mta;
+
+extern "C" {
+
+size_t mta_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int cq2, int ck2, int q_row_begin,
+                           int q_row_end, int dtype) {
+    (void)D; (void)ck; (void)ck2;
+    if (B <= 0 || H <= 0 || S <= 0 || cq < 1 || cq2 < 1 || q_row_begin < 0 || q_row_end > S ||
+        q_row_end <= q_row_begin || !dtype_ok(dtype))
+        return 0;
+    return 2 * make_plan(B, H, S, cq, cq2, q_row_begin, q_row_end, dtype).buf_bytes;
+}
+
+int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, const void* W1, const void* w2,
+                  const void* W2, void* o, void* workspace, size_t workspace_bytes, int B, int H, int S, int D, int cq,
+                  int ck, int cq2, int ck2, int q_row_begin, int q_row_end, int causal, int dtype, int w_dtype,
+                  void* stream) {
+    set_error("%s", "");
+    MTA_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "fused_fwd: unknown dtype code (%d, %d)", dtype, w_dtype);
+    MTA_REQUIRE(B >= 0 && H >= 1 && S >= 0 && D >= 1, "fused_fwd: bad shape B=%d H=%d S=%d D=%d", B, H, S, D);
+    MTA_REQUIRE(cq >= 1 && ck >= 1 && cq2 >= 1 && ck2 >= 1, "fused_fwd: kernel sizes must be positive");
+    MTA_REQUIRE(ck % 2 == 1 && ck2 % 2 == 1, "fused_fwd: key kernel sizes %d and %d must be odd (pad_key=\"both\")", ck, ck2);
+    MTA_REQUIRE(q_row_begin >= 0 && q_row_end <= S && q_row_begin <= q_row_end, "fused_fwd: row range [%d,%d) outside [0,%d)",
+                q_row_begin, q_row_end, S);
+    if ((long)B * S == 0 || q_row_begin == q_row_end) return MTA_OK;
+    MTA_REQUIRE(q && k && v && w1 && W1 && w2 && W2 && o, "fused_fwd: null pointer");
+    MTA_REQUIRE((long)B * H <= 65535, "fused_fwd: B*H = %ld exceeds 65535", (long)B * H);
+    const Plan pl = make_plan(B, H, S, cq, cq2, q_row_begin, q_row_end, dtype);
+    MTA_REQUIRE(workspace && workspace_bytes >= 2 * pl.buf_bytes, "fused_fwd: workspace of %zu bytes is smaller than the %zu needed",
+                workspace_bytes, 2 * pl.buf_bytes);
+    MTA_REQUIRE(aligned16(workspace), "fused_fwd: workspace must be 16-byte aligned");
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void* bufA = workspace;
+    void* bufB = static_cast<char*>(workspace) + pl.buf_bytes;
+    const PlaneView pv{(long)(pl.r1 - pl.ra) * S, pl.ra, S};
+    const long planes = (long)B * H;
+    const float scale = 1.0f / sqrtf((float)D);
+    const int round16 = dtype != MTA_F32;
+    int rc;
+    if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, scale, round16, causal, pl.ra, pl.r1, dtype, st))) return rc;
+    if ((rc = conv2d_launch(bufA, pv, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
+    if ((rc = head_linear_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.rb, pl.r1, false, dtype, st))) return rc;
+    if ((rc = softmax_launch(bufA, pv, bufA, pv, planes, S, S, causal, pl.rb, pl.r1, false, 1.0f, dtype, st))) return rc;
+    if ((rc = conv2d_launch(bufA, pv, w2, w_dtype, bufB, pv, planes, H, S, S, cq2, ck2, causal, pl.r0, pl.r1, !causal, dtype, st))) return rc;
+    if ((rc = head_linear_launch(bufB, pv, W2, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.r0, pl.r1, false, dtype, st))) return rc;
+    return pv_launch(bufA, pv, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st);
+}
+
+size_t mta_conv_attn_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int dtype) {
+    (void)D; (void)ck;
+    if (B <= 0 || H <= 0 || S <= 0 || cq < 1 || !dtype_ok(dtype)) return 0;
+    return 2 * make_plan(B, H, S, cq, 1, 0, S, dtype).buf_bytes;
+}
+
+int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w, void* o, void* workspace,
+                      size_t workspace_bytes, int B, int H, int S, int D, int cq, int ck, int causal, float scale,
+                      int dtype, int w_dtype, void* stream) {
+    set_error("%s", "");
+    MTA_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "conv_attn_fwd: unknown dtype code (%d, %d)", dtype, w_dtype);
+    MTA_REQUIRE(B >= 0 && H >= 1 && S >= 0 && D >= 1, "conv_attn_fwd: bad shape B=%d H=%d S=%d D=%d", B, H, S, D);
+    MTA_REQUIRE(cq >= 1 && ck >= 1 && ck % 2 == 1, "conv_attn_fwd: kernel size %dx%d needs an odd key extent", cq, ck);
+    if ((long)B * S == 0) return MTA_OK;
+    MTA_REQUIRE(q && k && v && w && o, "conv_attn_fwd: null pointer");
+    MTA_REQUIRE((long)B * H <= 65535, "conv_attn_fwd: B*H = %ld exceeds 65535", (long)B * H);
+    const Plan pl = make_plan(B, H, S, cq, 1, 0, S, dtype);
+    MTA_REQUIRE(workspace && workspace_bytes >= 2 * pl.buf_bytes, "conv_attn_fwd: workspace of %zu bytes is smaller than the %zu needed",
+                workspace_bytes, 2 * pl.buf_bytes);
+    MTA_REQUIRE(aligned16(workspace), "conv_attn_fwd: workspace must be 16-byte aligned");
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void* bufA = workspace;
+    void* bufB = static_cast<char*>(workspace) + pl.buf_bytes;
+    const PlaneView pv{(long)S * S, 0, S};
+    const long planes = (long)B * H;
+    int rc;
+    if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, 1.0f, 0, causal, 0, S, dtype, st))) return rc;
+    if ((rc = conv2d_launch(bufA, pv, w, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, 0, S, !causal, dtype, st))) return rc;
+    if ((rc = softmax_launch(bufB, pv, bufB, pv, planes, S, S, causal, 0, S, false, scale, dtype, st))) return rc;
+    return pv_launch(bufB, pv, v, o, B, H, S, D, causal, 0, S, dtype, st);
+}
+
+}  // extern "C"

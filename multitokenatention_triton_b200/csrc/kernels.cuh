@@ -1,0 +1,39 @@
+// Internal launch interface between the C ABI (abi.cu), the fused forward (fused.cu) and the kernel
+// translation units.  Every function enqueues work on `st` and returns an MTA_* status.
+#pragma once
+
+#include "common.cuh"
+
+namespace mta {
+
+// Depthwise causal conv over planes; computes output rows [row_begin,row_end) of every plane.
+// When `write_upper` the entries above the diagonal of those rows are written as 0, otherwise they
+// are left untouched (internal scratch whose upper triangle nobody reads).
+int conv2d_launch(const void* x, PlaneView xv, const void* w, int w_dtype, void* y, PlaneView yv, long planes,
+                  int C, int H, int W, int R, int S, int causal, int row_begin, int row_end, bool write_upper,
+                  int dtype, cudaStream_t st);
+
+// Head mix over groups of C planes; rows [row_begin,row_end).  `write_upper` as above (value `fill`).
+int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N,
+                       int C, int P, int Q, int causal, float fill, int row_begin, int row_end, bool write_upper,
+                       int dtype, cudaStream_t st);
+
+// Causal row softmax of pre_scale * x; rows [row_begin,row_end).
+int softmax_launch(const void* x, PlaneView xv, void* y, PlaneView yv, long planes, int P, int Q, int causal,
+                   int row_begin, int row_end, bool write_upper, float pre_scale, int dtype, cudaStream_t st);
+
+// s = round(round(Q K^T) * scale) for rows [row_begin,row_end), keys k <= q when causal.
+int qk_scores_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
+                     int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
+
+// o[rows] = p[rows, k<=q] V.
+int pv_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
+              int row_begin, int row_end, int dtype, cudaStream_t st);
+
+// CUDA-core versions of the two contractions (gemm_simt.cu).
+int qk_scores_simt_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
+                          int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
+int pv_simt_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
+                   int row_begin, int row_end, int dtype, cudaStream_t st);
+
+}  // namespace mta

@@ -1,0 +1,153 @@
+"""Functional front end of the CUDA library: one function per C-ABI entry point.
+
+Every function takes contiguous CUDA tensors, allocates its output (and scratch) with PyTorch and
+enqueues the kernels on PyTorch's current stream.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import MTALibraryError, check, dtype_code, lib, stream_ptr
+
+
+def _cuda_contig(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise MTALibraryError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _weight(w: torch.Tensor, like: torch.Tensor, name: str) -> torch.Tensor:
+    w = _cuda_contig(w.detach(), name)
+    if w.dtype not in (torch.float32, like.dtype):
+        w = w.to(like.dtype)
+    return w
+
+
+def conv2d_fwd(x: torch.Tensor, weight: torch.Tensor, causal: bool) -> torch.Tensor:
+    """Depthwise causal conv: x (N,C,H,W), weight (C,R,S) -> (N,C,H,W)."""
+    x = _cuda_contig(x, "input")
+    if x.dim() != 4 or weight.dim() != 3:
+        raise MTALibraryError(f"conv2d: expected input (N,C,H,W) and weight (C,R,S), got {tuple(x.shape)} and {tuple(weight.shape)}")
+    N, C, H, W = x.shape
+    Cw, R, S = weight.shape
+    assert C == Cw, "This implementation assumes depthwise convolution (C_in == C_out)"
+    w = _weight(weight, x, "weight")
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(lib().mta_conv2d_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, C, H, W, R, S, int(bool(causal)),
+                                   dtype_code(x), dtype_code(w), stream_ptr(x.device)), "mta_conv2d_fwd")
+    return y
+
+
+def head_linear_fwd(x: torch.Tensor, weight: torch.Tensor, causal: bool = True, output_value: float = 0.0) -> torch.Tensor:
+    """Head mix: x (N,C,P,Q), weight (C,C) -> (N,C,P,Q); entries with q > p become output_value when causal."""
+    x = _cuda_contig(x, "input")
+    if x.dim() != 4:
+        raise MTALibraryError(f"head_linear: expected input (N,C,P,Q), got {tuple(x.shape)}")
+    N, C, P, Q = x.shape
+    L = weight.shape[0]
+    assert weight.shape == (L, L), f"Weight must be square matrix, got {weight.shape}"
+    assert C == L, f"Channel dimension {C} must match weight dimension {L}"
+    w = _weight(weight, x, "weight")
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(lib().mta_head_linear_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, C, P, Q, int(bool(causal)),
+                                        float(output_value), dtype_code(x), dtype_code(w), stream_ptr(x.device)),
+              "mta_head_linear_fwd")
+    return y
+
+
+def softmax_fwd(x: torch.Tensor, causal: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 row softmax over keys q <= p; zeros above the diagonal.  x (N,C,P,Q)."""
+    x = _cuda_contig(x, "input")
+    N, C, P, Q = x.shape
+    y = torch.empty_like(x) if out is None else out
+    with torch.cuda.device(x.device):
+        check(lib().mta_softmax_fwd(x.data_ptr(), y.data_ptr(), N, C, P, Q, int(bool(causal)), dtype_code(x),
+                                    stream_ptr(x.device)), "mta_softmax_fwd")
+    return y
+
+
+def qk_scores_fwd(q: torch.Tensor, k: torch.Tensor, scale: float, causal: bool = True,
+                  round_like_reference: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(B,H,S,S) scores Q K^T * scale.  When causal, entries above the diagonal are zero."""
+    q, k = _cuda_contig(q, "q"), _cuda_contig(k, "k")
+    B, H, S, D = q.shape
+    if out is not None:
+        s = out      # entries above the diagonal keep whatever they held
+    elif causal:
+        s = torch.zeros(B, H, S, S, device=q.device, dtype=q.dtype)
+    else:
+        s = torch.empty(B, H, S, S, device=q.device, dtype=q.dtype)
+    with torch.cuda.device(q.device):
+        check(lib().mta_qk_scores_fwd(q.data_ptr(), k.data_ptr(), s.data_ptr(), B, H, S, D, float(scale),
+                                      int(round_like_reference and q.dtype != torch.float32), int(bool(causal)),
+                                      dtype_code(q), stream_ptr(q.device)), "mta_qk_scores_fwd")
+    return s
+
+
+def pv_fwd(p: torch.Tensor, v: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """(B,H,S,D) = P V, reading only keys k <= q of P when causal."""
+    p, v = _cuda_contig(p, "p"), _cuda_contig(v, "v")
+    B, H, S, D = v.shape
+    o = torch.empty_like(v)
+    with torch.cuda.device(v.device):
+        check(lib().mta_pv_fwd(p.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, S, D, int(bool(causal)), dtype_code(v),
+                               stream_ptr(v.device)), "mta_pv_fwd")
+    return o
+
+
+def conv_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weight: torch.Tensor, causal: bool,
+                  softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """softmax(scale * conv(Q K^T)) V with q,k,v (B,H,S,D), weight (H,cq,ck) -> (B,H,S,D)."""
+    q, k, v = _cuda_contig(q, "Q"), _cuda_contig(k, "K"), _cuda_contig(v, "V")
+    B, H, S, D = q.shape
+    Cw, cq, ck = weight.shape
+    assert Cw == H
+    assert k.shape == q.shape and v.shape == q.shape
+    if softmax_scale is None:
+        softmax_scale = 1.0 / (D ** 0.5)
+    w = _weight(weight, q, "weight")
+    o = torch.empty_like(q)
+    L = lib()
+    nbytes = L.mta_conv_attn_workspace_bytes(B, H, S, D, cq, ck, dtype_code(q))
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        check(L.mta_conv_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), o.data_ptr(), ws.data_ptr(),
+                                  nbytes, B, H, S, D, cq, ck, int(bool(causal)), float(softmax_scale), dtype_code(q),
+                                  dtype_code(w), stream_ptr(q.device)), "mta_conv_attn_fwd")
+    return o
+
+
+def mta_fused_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w1: torch.Tensor, W1: torch.Tensor,
+                  w2: torch.Tensor, W2: torch.Tensor, causal: bool = True,
+                  rows: Optional[Tuple[int, int]] = None, out: Optional[torch.Tensor] = None,
+                  workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Full four-stage MTA forward; returns (B,H,S,D) contiguous.  With `rows=(r0,r1)` only those query rows
+    of the output are written (the rest of a fresh output is zero)."""
+    q, k, v = _cuda_contig(q, "xq"), _cuda_contig(k, "xk"), _cuda_contig(v, "xv")
+    B, H, S, D = q.shape
+    assert k.shape == q.shape and v.shape == q.shape
+    w1, w2 = _weight(w1, q, "conv weight"), _weight(w2, q, "post-softmax conv weight")
+    W1, W2 = _weight(W1, q, "head-mix weight"), _weight(W2, q, "post-softmax head-mix weight")
+    wd = {w1.dtype, w2.dtype, W1.dtype, W2.dtype}
+    if len(wd) != 1:
+        w1, w2, W1, W2 = (t.float() for t in (w1, w2, W1, W2))
+    _, cq, ck = w1.shape
+    _, cq2, ck2 = w2.shape
+    r0, r1 = (0, S) if rows is None else rows
+    if out is None:
+        out = torch.empty_like(q) if (r0, r1) == (0, S) else torch.zeros_like(q)
+    L = lib()
+    nbytes = L.mta_workspace_bytes(B, H, S, D, cq, ck, cq2, ck2, r0, r1, dtype_code(q))
+    if workspace is None or workspace.numel() < nbytes:
+        workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        check(L.mta_fused_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), w1.data_ptr(), W1.data_ptr(), w2.data_ptr(),
+                              W2.data_ptr(), out.data_ptr(), workspace.data_ptr(), workspace.numel(), B, H, S, D, cq, ck,
+                              cq2, ck2, r0, r1, int(bool(causal)), dtype_code(q), dtype_code(w1), stream_ptr(q.device)),
+              "mta_fused_fwd")
+    return out

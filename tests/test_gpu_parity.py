@@ -1,0 +1,233 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle and the golden
+vectors made by the reference's PyTorch code, on the same seeded inputs.
+
+Tolerances are those of the parity contract (tests/util.py): float32 max abs error <= 1e-3; 16-bit
+dtypes <= 2e-2 relative, norm-wise.  Stand-alone ops are held to a much tighter bound because a single
+stage only differs from the oracle by summation order and one rounding.
+"""
+import numpy as np
+import pytest
+import torch
+
+from cases import CONV_ATTN_CASES, CONV_CASES, HEAD_CASES, MTA_CASES
+from multitokenatention_triton_b200 import (Conv2dTriton, MTAAttentionTriton, TritonConvAttention, TritonLinearHead,
+                                            _lib, ops)
+from multitokenatention_triton_b200.synthetic import make_conv_inputs, make_head_linear_inputs, make_mta_inputs
+from oracle import mta_oracle as orc
+from util import ROUND, assert_parity, max_abs, npf, rel_fro, rel_max
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ULP = {torch.float32: 2.0 ** -17, torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}
+
+
+def one_stage_close(out, ref, dtype, what):
+    """A single stage: fp32 accumulation then one rounding to the dtype -> at most ~1 ulp of the dtype
+    relative to the largest magnitude in play."""
+    tol = 2.0 * ULP[dtype] * max(1.0, float(np.max(np.abs(ref[np.isfinite(ref)]), initial=0.0)))
+    rel_fro(out, ref)   # non-finite pattern must match exactly
+    assert max_abs(out, ref) <= tol, f"{what}: max abs {max_abs(out, ref):.3e} > {tol:.3e}"
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", list(CONV_CASES))
+def test_conv2d(name, golden):
+    N, C, S, D, R, Sk, dtype, seed, causal = CONV_CASES[name]
+    inp = make_conv_inputs(N, C, S, D, R, Sk, dtype, seed)          # upper triangle left as computed
+    m = Conv2dTriton(C, (R, Sk), causal=causal).to(DEV).to(dtype)
+    with torch.no_grad():
+        m.weight.copy_(inp["w"])
+        y = m(inp["x"].to(DEV))
+    assert y.shape == inp["x"].shape and y.dtype == dtype
+    out = npf(y)
+    ref = orc.conv2d(npf(inp["x"]), npf(inp["w"]), causal, ROUND[dtype])
+    one_stage_close(out, ref, dtype, name)
+    one_stage_close(out, golden[f"conv/{name}"], dtype, name + " vs golden")
+    if causal:
+        iu = np.triu_indices(S, 1)
+        assert np.all(out[..., iu[0], iu[1]] == 0.0), "output above the diagonal must be exactly 0"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("S,R,Sk", [(7, 3, 3), (33, 1, 1), (96, 2, 7), (129, 6, 11), (200, 11, 15), (70, 20, 21)])
+def test_conv2d_fp32_weights_and_odd_shapes(S, R, Sk, dtype):
+    inp = make_conv_inputs(2, 3, S, 16, R, Sk, dtype, seed=1000 + S)
+    w32 = torch.randn(3, R, Sk, generator=torch.Generator().manual_seed(S)) * (R * Sk) ** -0.5   # weight kept in fp32
+    y = ops.conv2d_fwd(inp["x"].to(DEV), w32.to(DEV), True)
+    ref = orc.conv2d(npf(inp["x"]), npf(w32), True, ROUND[dtype])
+    one_stage_close(npf(y), ref, dtype, f"S={S} {R}x{Sk}")
+
+
+def test_conv2d_rectangular_noncausal():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 3, 37, 150, generator=g)
+    w = torch.randn(3, 4, 9, generator=g) / 6
+    y = ops.conv2d_fwd(x.to(DEV), w.to(DEV), False)
+    ref = orc.conv2d(npf(x), npf(w), False)
+    one_stage_close(npf(y), ref, torch.float32, "rectangular")
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("name", list(HEAD_CASES))
+def test_head_linear(name, variant, golden):
+    N, C, S, dtype, seed, causal, fill = HEAD_CASES[name]
+    mma_able = dtype != torch.float32 and C <= 32 and S % 8 == 0
+    if variant == 2 and not mma_able:
+        pytest.skip("tensor-core variant needs a 16-bit dtype, C <= 32 and S % 8 == 0")
+    inp = make_head_linear_inputs(N, C, S, dtype, seed)
+    m = TritonLinearHead(C, causal=causal, output_value=fill).to(DEV).to(dtype)
+    _lib.set_variant("head_linear", variant)
+    try:
+        with torch.no_grad():
+            m.weight.copy_(inp["W"])
+            y = m(inp["x"].to(DEV))
+    finally:
+        _lib.set_variant("head_linear", 0)
+    out = npf(y)
+    ref = orc.head_linear(npf(inp["x"]), npf(inp["W"]), causal, fill, ROUND[dtype])
+    one_stage_close(out, ref, dtype, name)
+    one_stage_close(out, golden[f"head/{name}"], dtype, name + " vs golden")
+    if causal:
+        iu = np.triu_indices(S, 1)
+        up = out[..., iu[0], iu[1]]
+        assert np.all(up == fill) if np.isfinite(fill) else np.all(np.isneginf(up))
+
+
+@pytest.mark.parametrize("C", [1, 2, 7, 12, 16, 24, 32, 48, 128])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_head_linear_head_counts(C, dtype):
+    S = 72
+    inp = make_head_linear_inputs(1, C, S, dtype, seed=300 + C, mix_var=0.2)
+    W32 = inp["W"].float() + 1e-3 * torch.randn(C, C, generator=torch.Generator().manual_seed(C))   # not bf16-representable
+    y = ops.head_linear_fwd(inp["x"].to(DEV), W32.to(DEV), True, float("-inf"))
+    ref = orc.head_linear(npf(inp["x"]), npf(W32), True, float("-inf"), ROUND[dtype])
+    one_stage_close(npf(y), ref, dtype, f"C={C}")
+
+
+def test_head_linear_ignores_input_above_diagonal():
+    inp = make_head_linear_inputs(1, 16, 128, torch.bfloat16, seed=77)
+    x = inp["x"].clone()
+    iu = torch.triu_indices(128, 128, 1)
+    x[..., iu[0], iu[1]] = float("nan")
+    y = ops.head_linear_fwd(x.to(DEV), inp["W"].to(DEV), True, 0.0)
+    ref = orc.head_linear(npf(inp["x"]), npf(inp["W"]), True, 0.0, orc.ROUND_BF16)
+    one_stage_close(npf(y), ref, torch.bfloat16, "nan above the diagonal")
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("S", [1, 5, 64, 130, 1000])
+def test_softmax(S, dtype):
+    g = torch.Generator().manual_seed(S)
+    x = (3 * torch.randn(2, 3, S, S, generator=g)).to(dtype)
+    y = ops.softmax_fwd(x.to(DEV), True)
+    ref = orc.softmax(npf(x), True, ROUND[dtype])
+    one_stage_close(npf(y), ref, dtype, f"softmax S={S}")
+    xm = x.clone()
+    xm[..., torch.triu_indices(S, S, 1)[0], torch.triu_indices(S, S, 1)[1]] = float("-inf")
+    y2 = ops.softmax_fwd(xm.to(DEV), False)      # the -inf filled tensor of the reference, full rows
+    one_stage_close(npf(y2), ref, dtype, f"softmax of -inf filled S={S}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("S,D", [(5, 8), (65, 16), (130, 64), (256, 128)])
+def test_contractions(S, D, dtype):
+    g = torch.Generator().manual_seed(S + D)
+    q, k, v = (torch.randn(2, 3, S, D, generator=g).to(dtype) for _ in range(3))
+    s = ops.qk_scores_fwd(q.to(DEV), k.to(DEV), D ** -0.5, True)
+    ref = torch.tril(torch.matmul(q.double(), k.double().transpose(2, 3)))
+    if dtype == torch.float32:
+        ref = ref * D ** -0.5
+    else:   # matmul rounded, times the rounded scale, rounded (mta_attention_pytorch.py:63-65)
+        ref = (ref.to(dtype).double() * torch.tensor(D ** -0.5).to(dtype).double()).to(dtype).double()
+    one_stage_close(npf(s), ref.float().numpy(), dtype, "scores")
+    p = torch.tril(torch.softmax(torch.randn(2, 3, S, S, generator=g), -1)).to(dtype)
+    o = ops.pv_fwd(p.to(DEV), v.to(DEV), True)
+    oref = torch.matmul(p.double(), v.double())
+    one_stage_close(npf(o), oref.float().numpy(), dtype, "pv")
+
+
+# ---------------------------------------------------------------------------------------------
+def build_mta(wl, inp, fused):
+    import types
+    cfg = types.SimpleNamespace(use_mta=True, query_kernel_size=wl.cq, key_kernel_size=wl.ck,
+                                after_sm_query_kernel_size=wl.cq2, after_sm_key_kernel_size=wl.ck2,
+                                pre_sm_linear_head=True, post_sm_linear_head=True, pad_key="both",
+                                init_method="identity", dim=wl.H * wl.D)
+    m = MTAAttentionTriton(wl.H, cfg, dropout=0.0, causal=True, fused=fused).to(DEV).to(wl.dtype).eval()
+    with torch.no_grad():
+        m.mta_conv_triton.weight.copy_(inp["w1"])
+        m.wpsm_triton.weight.copy_(inp["W1"])
+        m.mta_conv_after_sm_triton.weight.copy_(inp["w2"])
+        m.wposm_triton.weight.copy_(inp["W2"])
+    return m
+
+
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("name", list(MTA_CASES))
+def test_mta_forward(name, fused, golden):
+    wl = MTA_CASES[name]
+    inp = make_mta_inputs(wl)
+    m = build_mta(wl, inp, fused)
+    with torch.no_grad():
+        out = m(inp["q"].to(DEV), inp["k"].to(DEV), inp["v"].to(DEV), None, None)
+    assert out.shape == (wl.B, wl.S, wl.H, wl.D) and out.dtype == wl.dtype
+    assert not out.is_contiguous() or wl.S == 1 or wl.H == 1     # the (B,S,H,D) transpose view, as the reference returns
+    got = npf(out.transpose(1, 2))
+    a = [npf(inp[k]) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    exact = orc.mta_fwd(*a, True, orc.ROUND_NONE)
+    assert_parity(got, exact, wl.dtype, f"{name} vs oracle")
+    assert_parity(got, golden[f"mta/{name}"], wl.dtype, f"{name} vs golden")
+    if wl.dtype != torch.float32:
+        staged = orc.mta_fwd(*a, True, ROUND[wl.dtype])
+        assert_parity(got, staged, wl.dtype, f"{name} vs stage-rounded oracle")
+
+
+@pytest.mark.parametrize("name,rows", [("ragged_f32", (3, 20)), ("ragged_f32", (64, 65)), ("s130_6x11_bf16", (17, 130)),
+                                       ("c1", (100, 164)), ("s192_h32_f16", (0, 9))])
+def test_mta_forward_row_range(name, rows):
+    wl = MTA_CASES[name]
+    inp = make_mta_inputs(wl)
+    d = {k: t.to(DEV) for k, t in inp.items()}
+    full = ops.mta_fused_fwd(d["q"], d["k"], d["v"], d["w1"], d["W1"], d["w2"], d["W2"], True)
+    out = torch.full_like(full, 7.0)
+    ops.mta_fused_fwd(d["q"], d["k"], d["v"], d["w1"], d["W1"], d["w2"], d["W2"], True, rows=rows, out=out)
+    r0, r1 = rows
+    assert torch.equal(out[:, :, r0:r1], full[:, :, r0:r1]), "a row range must reproduce the rows of the full forward"
+    assert torch.all(out[:, :, :r0] == 7.0) and torch.all(out[:, :, r1:] == 7.0), "rows outside the range must not be written"
+    a = [npf(inp[k]) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    ref = orc.mta_fwd_rows(*a, 0, r0, r1, True, orc.ROUND_NONE)
+    assert_parity(npf(out[0, :, r0:r1]), ref, wl.dtype, f"{name} rows {rows}")
+
+
+@pytest.mark.parametrize("name", list(CONV_ATTN_CASES))
+def test_conv_attention(name, golden):
+    wl, causal = CONV_ATTN_CASES[name]
+    inp = make_mta_inputs(wl)
+    m = TritonConvAttention(wl.H, (wl.cq, wl.ck), causal=causal).to(DEV).to(wl.dtype)
+    with torch.no_grad():
+        m.weight.copy_(inp["w1"])
+        res = m(inp["q"].to(DEV), inp["k"].to(DEV), inp["v"].to(DEV), causal, wl.D ** -0.5)
+    out = res[0]
+    assert out.shape == (wl.B, wl.H, wl.S, wl.D)
+    a = [npf(inp[k]) for k in ("q", "k", "v", "w1")]
+    ref = orc.conv_attn_fwd(*a, causal, None, orc.ROUND_NONE)
+    assert_parity(npf(out), ref, wl.dtype, f"{name} vs oracle")
+    assert_parity(npf(out), golden[f"conv_attn/{name}"], wl.dtype, f"{name} vs golden")
+
+
+def test_error_paths_on_device():
+    x = torch.zeros(1, 2, 8, 8, device=DEV)
+    with pytest.raises(AssertionError):
+        ops.head_linear_fwd(x, torch.eye(3, device=DEV))
+    with pytest.raises(_lib.MTALibraryError):
+        ops.head_linear_fwd(torch.zeros(1, 200, 8, 8, device=DEV), torch.eye(200, device=DEV))
+    with pytest.raises(_lib.MTALibraryError):
+        ops.conv2d_fwd(x.to(torch.float64), torch.zeros(2, 3, 3, device=DEV, dtype=torch.float64), True)
+    with pytest.raises(_lib.MTALibraryError):   # even key kernel
+        q = torch.zeros(1, 2, 8, 8, device=DEV)
+        ops.mta_fused_fwd(q, q, q, torch.zeros(2, 3, 4, device=DEV), torch.eye(2, device=DEV),
+                          torch.zeros(2, 3, 3, device=DEV), torch.eye(2, device=DEV))
+    # the context is still healthy
+    assert torch.isfinite(ops.softmax_fwd(torch.randn(1, 1, 8, 8, device=DEV))).all()
