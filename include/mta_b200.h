@@ -64,7 +64,7 @@ int mta_head_linear_fwd(const void* x, const void* Wm, void* y, int N, int C, in
 int mta_softmax_fwd(const void* x, void* y, int N, int C, int P, int Q, int causal, int dtype, void* stream);
 
 /*
- * Scaled scores Q K^T * scale for keys k <= q (entries above the diagonal are left untouched when
+ * Scaled scores Q K^T * scale for keys k <= q (entries above the diagonal are never written when
  * causal) and P V over keys k <= q.  They stand in for the two torch.matmul calls of
  * MTAAttentionTriton.forward (mta_attention_triton.py:68-71, :89).  q,k,v,o: (B,H,S,D); s,p: (B,H,S,S).
  * `round_scale` != 0 reproduces the reference's 16-bit rounding (matmul result rounded, then
@@ -106,13 +106,20 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
                   int cq, int ck, int cq2, int ck2, int q_row_begin, int q_row_end, int causal, int dtype,
                   int w_dtype, void* stream);
 
+/*
+ * Synchronises `stream` and reports whether any kernel launched on this device since the last call gave
+ * up a bounded device-side wait (returns 4 and clears the flag) - kernels never spin without limit.
+ */
+int mta_device_status(void* stream);
+
 /* Number of kernel launches issued by this library on the calling thread since the last reset
  * (what a benchmark reports as its launch count). */
 long mta_launch_count(void);
 void mta_reset_launch_count(void);
 
 /* Selects implementation variants for A/B measurement: key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core;
- * key "conv2d" -> 0 auto, 1 CUDA-core, 2 tensor-core.  Returns 0, or 1 for an unknown key/value. */
+ * key "conv2d" -> 0 auto, 1 CUDA-core, 2 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core,
+ * 2 tcgen05 tensor-core.  Returns 0, or 1 for an unknown key/value. */
 int mta_set_variant(const char* key, int value);
 
 #ifdef __cplusplus

@@ -26,6 +26,7 @@ SIGNATURES = {
     "mta_launch_count": (ctypes.c_long, []),
     "mta_reset_launch_count": (None, []),
     "mta_set_variant": (_i, [ctypes.c_char_p, _i]),
+    "mta_device_status": (_i, [_vp]),
     "mta_conv2d_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "mta_head_linear_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_softmax_fwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
@@ -75,6 +76,13 @@ def dtype_code(t: torch.Tensor) -> int:
 
 def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def device_status(device=None) -> None:
+    """Synchronises the current stream and raises if a device-side bounded wait gave up."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        check(lib().mta_device_status(stream_ptr(dev)), "mta_device_status")
 
 
 def set_variant(key: str, value: int) -> None:

@@ -128,7 +128,18 @@ int mta_pv_fwd(const void* p, const void* v, void* o, int B, int H, int S, int D
     MTA_REQUIRE(p && v && o, "pv: null pointer");
     MTA_REQUIRE((long)B * H <= 65535, "pv: B*H = %ld exceeds 65535", (long)B * H);
     if (int rc = check_device()) return rc;
-    return pv_launch(p, full_view(S, S), v, o, B, H, S, D, causal ? 1 : 0, 0, S, dtype, static_cast<cudaStream_t>(stream));
+    return pv_launch(p, full_view(S, S), S, v, o, B, H, S, D, causal ? 1 : 0, 0, S, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int mta_device_status(void* stream) {
+    g_error[0] = 0;
+    int timed_out = 0;
+    if (int rc = device_wait_status(static_cast<cudaStream_t>(stream), &timed_out)) return rc;
+    if (timed_out) {
+        set_error("a device-side bounded wait (mbarrier) gave up: results of the kernels launched since the last check are invalid");
+        return MTA_ERR_TIMEOUT;
+    }
+    return MTA_OK;
 }
 
 }  // extern "C"

@@ -26,14 +26,23 @@ int softmax_launch(const void* x, PlaneView xv, void* y, PlaneView yv, long plan
 int qk_scores_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
                      int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 
-// o[rows] = p[rows, k<=q] V.
-int pv_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
-              int row_begin, int row_end, int dtype, cudaStream_t st);
+// o[rows] = p[rows, k<=q] V.  `p_rows_stored` = number of rows each plane of p holds (from pview.row0 on).
+int pv_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
+              int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 
 // CUDA-core versions of the two contractions (gemm_simt.cu).
 int qk_scores_simt_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
                           int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 int pv_simt_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
                    int row_begin, int row_end, int dtype, cudaStream_t st);
+
+// tcgen05 tensor-core versions (gemm_tc05.cu): 16-bit dtypes, D in {64,128}, S a multiple of 8.
+bool tc05_contractions_supported(int S, int D, int dtype, const void* a, const void* b, const void* c, PlaneView view);
+int qk_scores_tc05_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
+                          int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
+int pv_tc05_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
+                   int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
+// Reads and clears the flag raised by a device-side bounded wait that gave up (synchronises `st`).
+int device_wait_status(cudaStream_t st, int* timed_out);
 
 }  // namespace mta

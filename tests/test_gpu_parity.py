@@ -130,9 +130,22 @@ def test_softmax(S, dtype):
     one_stage_close(npf(y2), ref, dtype, f"softmax of -inf filled S={S}")
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,D", [(5, 8), (65, 16), (130, 64), (256, 128)])
-def test_contractions(S, D, dtype):
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("S,D", [(5, 8), (65, 16), (130, 64), (256, 128), (128, 64), (200, 128), (8, 64), (1000, 128)])
+def test_contractions(S, D, dtype, variant):
+    """variant 1 = CUDA-core kernels, 2 = tcgen05 tensor-core kernels (16-bit dtypes, D in {64,128}, S % 8 == 0)."""
+    if variant == 2 and (dtype == torch.float32 or D not in (64, 128) or S % 8):
+        pytest.skip("outside the tensor-core kernels' domain")
+    _lib.set_variant("gemm", variant)
+    try:
+        _contractions(S, D, dtype)
+        _lib.device_status()
+    finally:
+        _lib.set_variant("gemm", 0)
+
+
+def _contractions(S, D, dtype):
     g = torch.Generator().manual_seed(S + D)
     q, k, v = (torch.randn(2, 3, S, D, generator=g).to(dtype) for _ in range(3))
     s = ops.qk_scores_fwd(q.to(DEV), k.to(DEV), D ** -0.5, True)
@@ -143,9 +156,18 @@ def test_contractions(S, D, dtype):
         ref = (ref.to(dtype).double() * torch.tensor(D ** -0.5).to(dtype).double()).to(dtype).double()
     one_stage_close(npf(s), ref.float().numpy(), dtype, "scores")
     p = torch.tril(torch.softmax(torch.randn(2, 3, S, S, generator=g), -1)).to(dtype)
-    o = ops.pv_fwd(p.to(DEV), v.to(DEV), True)
+    pg = p.clone()
+    iu = torch.triu_indices(S, S, 1)
+    pg[..., iu[0], iu[1]] = float("nan")           # whatever sits above the diagonal must not be read
+    o = ops.pv_fwd(pg.to(DEV), v.to(DEV), True)
     oref = torch.matmul(p.double(), v.double())
     one_stage_close(npf(o), oref.float().numpy(), dtype, "pv")
+    # non-causal: full rows
+    pf = torch.softmax(torch.randn(2, 3, S, S, generator=g), -1).to(dtype)
+    o2 = ops.pv_fwd(pf.to(DEV), v.to(DEV), False)
+    one_stage_close(npf(o2), torch.matmul(pf.double(), v.double()).float().numpy(), dtype, "pv non-causal")
+    s2 = ops.qk_scores_fwd(q.to(DEV), k.to(DEV), 1.0, False, round_like_reference=False)
+    one_stage_close(npf(s2), torch.matmul(q.double(), k.double().transpose(2, 3)).float().numpy(), dtype, "scores non-causal")
 
 
 # ---------------------------------------------------------------------------------------------
