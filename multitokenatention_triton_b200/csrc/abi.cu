@@ -77,7 +77,7 @@ int mta_conv2d_fwd(const void* x, const void* w, void* y, int N, int C, int H, i
     MTA_REQUIRE(x != y, "conv2d: in-place operation is not supported");
     if (int rc = check_device()) return rc;
     const PlaneView v = full_view(H, W);
-    return conv2d_launch(x, v, w, w_dtype, y, v, (long)N * C, C, H, W, R, S, causal ? 1 : 0, 0, H, true, x_dtype,
+    return conv2d_launch(x, v, H, w, w_dtype, y, v, (long)N * C, C, H, W, R, S, causal ? 1 : 0, 0, H, true, x_dtype,
                          static_cast<cudaStream_t>(stream));
 }
 

@@ -74,10 +74,10 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     const int round16 = dtype != MTA_F32;
     int rc;
     if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, scale, round16, causal, pl.ra, pl.r1, dtype, st))) return rc;
-    if ((rc = conv2d_launch(bufA, pv, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
+    if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
     if ((rc = head_linear_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.rb, pl.r1, false, dtype, st))) return rc;
     if ((rc = softmax_launch(bufA, pv, bufA, pv, planes, S, S, causal, pl.rb, pl.r1, false, 1.0f, dtype, st))) return rc;
-    if ((rc = conv2d_launch(bufA, pv, w2, w_dtype, bufB, pv, planes, H, S, S, cq2, ck2, causal, pl.r0, pl.r1, !causal, dtype, st))) return rc;
+    if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w2, w_dtype, bufB, pv, planes, H, S, S, cq2, ck2, causal, pl.r0, pl.r1, !causal, dtype, st))) return rc;
     if ((rc = head_linear_launch(bufB, pv, W2, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.r0, pl.r1, false, dtype, st))) return rc;
     return pv_launch(bufA, pv, pl.r1 - pl.ra, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st);
 }
@@ -110,7 +110,7 @@ int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w
     const long planes = (long)B * H;
     int rc;
     if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, 1.0f, 0, causal, 0, S, dtype, st))) return rc;
-    if ((rc = conv2d_launch(bufA, pv, w, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, 0, S, !causal, dtype, st))) return rc;
+    if ((rc = conv2d_launch(bufA, pv, S, w, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, 0, S, !causal, dtype, st))) return rc;
     if ((rc = softmax_launch(bufB, pv, bufB, pv, planes, S, S, causal, 0, S, false, scale, dtype, st))) return rc;
     return pv_launch(bufB, pv, S, v, o, B, H, S, D, causal, 0, S, dtype, st);
 }

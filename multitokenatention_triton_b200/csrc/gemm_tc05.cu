@@ -48,7 +48,8 @@ int wait_flag_ptr(int** out) {
 }
 
 int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
-                       uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_rows) {
+                       uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_cols, uint32_t box_rows,
+                       bool swizzle128) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -58,10 +59,13 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint
                 "tensor map: base and pitches must be multiples of 16 bytes");
     cuuint64_t dims[3] = {cols, rows, planes};
     cuuint64_t strides[2] = {row_pitch_elems * 2, plane_pitch_elems * 2};
-    cuuint32_t box[3] = {64, box_rows, 1};
+    MTA_REQUIRE(box_cols <= 256 && box_rows <= 256 && (box_cols * 2) % 16 == 0 && (!swizzle128 || box_cols == 64),
+                "tensor map: box %u x %u is not supported", box_cols, box_rows);
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -352,8 +356,8 @@ int launch_qk(const void* q, const void* k, void* s, PlaneView sv, int B, int H,
               int causal, int row_begin, int row_end, cudaStream_t st) {
     CUtensorMap mq, mk;
     int rc;
-    if ((rc = make_tensor_map_3d(&mq, q, (uint64_t)B * H, S, D, D, (uint64_t)S * D, TILE))) return rc;
-    if ((rc = make_tensor_map_3d(&mk, k, (uint64_t)B * H, S, D, D, (uint64_t)S * D, TILE))) return rc;
+    if ((rc = make_tensor_map_3d(&mq, q, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
+    if ((rc = make_tensor_map_3d(&mk, k, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
     int* flag = nullptr;
     if ((rc = wait_flag_ptr(&flag))) return rc;
     const int n_qt = (row_end - row_begin + TILE - 1) / TILE, all_k = (S + TILE - 1) / TILE;
@@ -376,8 +380,8 @@ int launch_pv(const void* p, PlaneView pview, const void* v, void* o, int B, int
               int row_end, long p_rows_stored, cudaStream_t st) {
     CUtensorMap mp, mv;
     int rc;
-    if ((rc = make_tensor_map_3d(&mp, p, (uint64_t)B * H, (uint64_t)p_rows_stored, S, S, (uint64_t)pview.plane_stride, TILE))) return rc;
-    if ((rc = make_tensor_map_3d(&mv, v, (uint64_t)B * H, S, D, D, (uint64_t)S * D, TILE))) return rc;
+    if ((rc = make_tensor_map_3d(&mp, p, (uint64_t)B * H, (uint64_t)p_rows_stored, S, S, (uint64_t)pview.plane_stride, 64, TILE, true))) return rc;
+    if ((rc = make_tensor_map_3d(&mv, v, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
     int* flag = nullptr;
     if ((rc = wait_flag_ptr(&flag))) return rc;
     const int n_qt = (row_end - row_begin + TILE - 1) / TILE;

@@ -9,9 +9,15 @@ namespace mta {
 // Depthwise causal conv over planes; computes output rows [row_begin,row_end) of every plane.
 // When `write_upper` the entries above the diagonal of those rows are written as 0, otherwise they
 // are left untouched (internal scratch whose upper triangle nobody reads).
-int conv2d_launch(const void* x, PlaneView xv, const void* w, int w_dtype, void* y, PlaneView yv, long planes,
-                  int C, int H, int W, int R, int S, int causal, int row_begin, int row_end, bool write_upper,
-                  int dtype, cudaStream_t st);
+// `x_rows_stored` = rows each plane of x holds (from xv.row0 on).
+int conv2d_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
+                  long planes, int C, int H, int W, int R, int S, int causal, int row_begin, int row_end,
+                  bool write_upper, int dtype, cudaStream_t st);
+// Tensor-core version (conv2d_mma.cu): 16-bit dtypes, S <= 17, W a multiple of 8, 16-byte aligned planes.
+bool conv2d_mma_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int W, int R, int S, int dtype);
+int conv2d_mma_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
+                      long planes, int C, int H, int W, int R, int S, int causal, int row_begin, int row_end,
+                      bool write_upper, int dtype, cudaStream_t st);
 
 // Head mix over groups of C planes; rows [row_begin,row_end).  `write_upper` as above (value `fill`).
 int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N,

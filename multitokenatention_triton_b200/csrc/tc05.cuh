@@ -143,11 +143,13 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // ---- host side: tensor maps ------------------------------------------------------------------------
 // 3-D map over [planes][rows][cols] of 16-bit elements (cols contiguous, row pitch `row_pitch_elems`, plane pitch
-// `plane_pitch_elems`), box = 64 cols x box_rows rows x 1 plane, 128-byte swizzle, out-of-bounds reads give zero.
+// `plane_pitch_elems`), box = box_cols x box_rows x 1 plane, with the 128-byte swizzle (box_cols must be 64) or
+// without a swizzle; out-of-bounds reads give zero.
 // Device address of the word that bounded waits raise on timeout (one per device, owned by the library).
 int wait_flag_ptr(int** out);
 
 int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
-                       uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_rows);
+                       uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_cols, uint32_t box_rows,
+                       bool swizzle128);
 
 }  // namespace mta

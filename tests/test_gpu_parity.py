@@ -30,14 +30,27 @@ def one_stage_close(out, ref, dtype, what):
 
 
 # ---------------------------------------------------------------------------------------------
+def conv_mma_able(dtype, S, Sk):
+    return dtype != torch.float32 and Sk <= 17 and S % 8 == 0
+
+
+@pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("name", list(CONV_CASES))
-def test_conv2d(name, golden):
+def test_conv2d(name, variant, golden):
+    """variant 1 = CUDA-core kernel, 2 = tensor-core (Toeplitz MMA + TMA) kernel."""
     N, C, S, D, R, Sk, dtype, seed, causal = CONV_CASES[name]
+    if variant == 2 and not conv_mma_able(dtype, S, Sk):
+        pytest.skip("outside the tensor-core kernel's domain")
     inp = make_conv_inputs(N, C, S, D, R, Sk, dtype, seed)          # upper triangle left as computed
     m = Conv2dTriton(C, (R, Sk), causal=causal).to(DEV).to(dtype)
-    with torch.no_grad():
-        m.weight.copy_(inp["w"])
-        y = m(inp["x"].to(DEV))
+    _lib.set_variant("conv2d", variant)
+    try:
+        with torch.no_grad():
+            m.weight.copy_(inp["w"])
+            y = m(inp["x"].to(DEV))
+        _lib.device_status()
+    finally:
+        _lib.set_variant("conv2d", 0)
     assert y.shape == inp["x"].shape and y.dtype == dtype
     out = npf(y)
     ref = orc.conv2d(npf(inp["x"]), npf(inp["w"]), causal, ROUND[dtype])
@@ -55,6 +68,26 @@ def test_conv2d_fp32_weights_and_odd_shapes(S, R, Sk, dtype):
     w32 = torch.randn(3, R, Sk, generator=torch.Generator().manual_seed(S)) * (R * Sk) ** -0.5   # weight kept in fp32
     y = ops.conv2d_fwd(inp["x"].to(DEV), w32.to(DEV), True)
     ref = orc.conv2d(npf(inp["x"]), npf(w32), True, ROUND[dtype])
+    one_stage_close(npf(y), ref, dtype, f"S={S} {R}x{Sk}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("S,R,Sk,causal", [(512, 6, 11, True), (264, 3, 3, True), (136, 1, 1, True), (320, 11, 15, True),
+                                             (200, 2, 17, True), (128, 4, 4, True), (384, 6, 11, False), (8, 3, 3, True)])
+def test_conv2d_tensor_core(S, R, Sk, causal, dtype):
+    """The Toeplitz-MMA kernel on larger planes, with NaN planted above the diagonal (must never be read)."""
+    inp = make_conv_inputs(2, 3, S, 32, R, Sk, dtype, seed=2000 + S + R)
+    x = inp["x"].clone()
+    if causal:
+        iu = torch.triu_indices(S, S, 1)
+        x[..., iu[0], iu[1]] = float("nan")
+    _lib.set_variant("conv2d", 2)
+    try:
+        y = ops.conv2d_fwd(x.to(DEV), inp["w"].to(DEV), causal)
+        _lib.device_status()
+    finally:
+        _lib.set_variant("conv2d", 0)
+    ref = orc.conv2d(npf(torch.tril(inp["x"]) if causal else inp["x"]), npf(inp["w"]), causal, ROUND[dtype])
     one_stage_close(npf(y), ref, dtype, f"S={S} {R}x{Sk}")
 
 
