@@ -176,19 +176,21 @@ def event_time_ms(fn, iters: int) -> float:
 def stage_breakdown(wl: MTAWorkload, d, peaks):
     """Times every kernel of the step alone (CUDA events on the launching stream, 3 warm-up + 5 timed launches;
     each launch streams gigabytes, far more than L2) and returns the list plus the roofline entry of the slowest.
-    Algorithmic traffic of a score-plane stage: read the lower triangle once and write it once."""
+    Algorithmic traffic of a score-plane stage as the stand-alone entry points run it: read the lower triangle
+    once and write the whole output plane (the zero / fill above the diagonal is part of what the call returns)."""
     from multitokenatention_triton_b200 import ops
     es = d["q"].element_size()
     lower = wl.lower_elements()
+    plane_bytes = float(es) * (lower + wl.B * wl.H * wl.S * wl.S)      # read lower + write full
     scale = wl.D ** -0.5
     s = ops.qk_scores_fwd(d["q"], d["k"], scale, True)
     c1 = ops.conv2d_fwd(s, d["w1"], True)
     stages = [
         ("qk_scores", lambda: ops.qk_scores_fwd(d["q"], d["k"], scale, True, out=s), "tensor", 2.0 * wl.D * lower),
-        ("conv1", lambda: ops.conv2d_fwd(s, d["w1"], True), "hbm", 2.0 * es * lower),
-        ("head_mix1", lambda: ops.head_linear_fwd(c1, d["W1"], True, 0.0), "hbm", 2.0 * es * lower),
-        ("softmax", lambda: ops.softmax_fwd(c1, True), "hbm", 2.0 * es * lower),
-        ("conv2", lambda: ops.conv2d_fwd(s, d["w2"], True), "hbm", 2.0 * es * lower),
+        ("conv1", lambda: ops.conv2d_fwd(s, d["w1"], True), "hbm", plane_bytes),
+        ("head_mix1", lambda: ops.head_linear_fwd(c1, d["W1"], True, 0.0), "hbm", plane_bytes),
+        ("softmax", lambda: ops.softmax_fwd(c1, True), "hbm", plane_bytes),
+        ("conv2", lambda: ops.conv2d_fwd(s, d["w2"], True), "hbm", plane_bytes),
         ("pv", lambda: ops.pv_fwd(c1, d["v"], True), "tensor", 2.0 * wl.D * lower),
     ]
     out = []

@@ -118,7 +118,7 @@ long mta_launch_count(void);
 void mta_reset_launch_count(void);
 
 /* Selects implementation variants for A/B measurement: key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core;
- * key "conv2d" -> 0 auto, 1 CUDA-core, 2 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core,
+ * key "conv2d" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core, 3 tcgen05 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core,
  * 2 tcgen05 tensor-core.  Returns 0, or 1 for an unknown key/value. */
 int mta_set_variant(const char* key, int value);
 

@@ -58,7 +58,7 @@ long mta_launch_count(void) { return g_launches; }
 void mta_reset_launch_count(void) { g_launches = 0; }
 
 int mta_set_variant(const char* key, int value) {
-    if (!key || value < 0 || value > 2) return MTA_ERR_INVALID;
+    if (!key || value < 0 || value > 3) return MTA_ERR_INVALID;
     if (!strcmp(key, "head_linear")) g_variant_head_linear = value;
     else if (!strcmp(key, "conv2d")) g_variant_conv2d = value;
     else if (!strcmp(key, "gemm")) g_variant_gemm = value;

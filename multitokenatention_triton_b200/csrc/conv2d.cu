@@ -5,7 +5,7 @@
 // where xh is x inside the plane and 0 outside it and, when causal, 0 wherever key > query.  The input
 // above the diagonal is therefore never read, and the output above the diagonal is 0.
 //
-// Kernel in this file (the tensor-core kernel for 16-bit dtypes is in conv2d_mma.cu):
+// Kernel in this file (the tensor-core kernels for 16-bit dtypes are in conv2d_tc05.cu and conv2d_mma.cu):
 //   conv2d_tile_kernel   any dtype, any R x S, any plane size.  A CTA owns a TM x TN output tile, stages
 //                        the (TM+R-1) x (TN+S-1) halo tile in shared memory as fp32 with the causal zero
 //                        applied on the way in, and every thread keeps a sliding register window along
@@ -122,9 +122,16 @@ int conv2d_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w
                   long planes, int C, int H, int W, int R, int S, int causal, int row_begin, int row_end,
                   bool write_upper, int dtype, cudaStream_t st) {
     if (planes == 0 || row_end <= row_begin || W == 0) return MTA_OK;
-    const int want = variant("conv2d");
+    const int want = variant("conv2d");      // 0 auto, 1 CUDA cores, 2 mma.sync tensor cores, 3 tcgen05 tensor cores
     const bool mma_ok = planes <= 65535 && conv2d_mma_supported(x, xv, y, yv, W, R, S, dtype);
-    MTA_REQUIRE(want != 2 || mma_ok, "conv2d: the tensor-core variant needs a 16-bit dtype, S <= 17, W %% 8 == 0 and 16-byte aligned planes");
+    const bool tc05_ok = planes <= 65535 && conv2d_tc05_supported(x, xv, y, yv, W, R, S, dtype, w_dtype);
+    MTA_REQUIRE(want != 2 || mma_ok, "conv2d: the mma.sync variant needs a 16-bit dtype, S <= 17, W %% 8 == 0 and 16-byte aligned planes");
+    MTA_REQUIRE(want != 3 || tc05_ok, "conv2d: the tcgen05 variant needs a 16-bit dtype, S <= 17, few row taps, W %% 8 == 0 and 16-byte aligned planes");
+    // Measured on the 6 x 11 bf16 case (B4 H16 S2048): mma.sync kernel 274 us, tcgen05 kernel 394 us - the tcgen05
+    // kernel is bound by shared-memory traffic (54 operand fetches of 4 KB per tile), so it is not the default.
+    if (tc05_ok && want == 3)
+        return conv2d_tc05_launch(x, xv, x_rows_stored, w, w_dtype, y, yv, planes, C, H, W, R, S, causal, row_begin,
+                                  row_end, write_upper, dtype, st);
     if (mma_ok && want != 1)
         return conv2d_mma_launch(x, xv, x_rows_stored, w, w_dtype, y, yv, planes, C, H, W, R, S, causal, row_begin,
                                  row_end, write_upper, dtype, st);

@@ -1,0 +1,510 @@
+// Depthwise causal conv over score planes on the tcgen05 tensor cores, 16-bit dtypes, key extent S <= 17.
+//
+// Toeplitz formulation (as in conv2d_mma.cu): for a fixed row tap i the key-direction taps form a banded matrix,
+//   out[q, k] += sum_kk X[q + i - (R-1), kk] * T_i[kk, k],   T_i[kk, k] = w[i, kk - k + pad_w]  (0 outside the band)
+// so every row tap and every block of 16 output columns costs two tcgen05 MMAs (M = 128 query rows, N = 16,
+// K = 16) of the staged input tile (rows shifted by i) against the two 16x16 slices of T_i.  The legacy mma.sync
+// pipe saturates on this op (measured); tcgen05 does not.
+//
+// Persistent, warp-specialised kernel: one CTA per SM walks a contiguous range of 128 x 128 output tiles
+// (only tiles that touch keys <= query when causal):
+//   warp 0      TMA producer: one tiled load per tile of the (128 + R-1) x 152 halo tile, row-major, into a
+//               2-stage ring (out-of-range rows / columns arrive as zero = the conv's zero padding)
+//   warps 2-5   repack the tile into the layout the MMA reads, zeroing keys above the causal diagonal on the
+//               way (2-stage ring); rebuild the Toeplitz slices when the head changes
+//   warp 1      issues the MMAs (54 per tile for a 6 x 11 kernel) into TMEM accumulator n % 2
+//   warps 6-9   epilogue: TMEM -> registers -> 16-bit -> swizzled shared-memory tile -> TMA tiled store (a thread
+//               owns one output row, so direct global stores would touch 32 different lines per instruction)
+//
+// MMA schedule.  Staged column sc holds key n0 - 8 + sc; output column x reads staged columns x + a_off + j
+// (a_off = 8 - pad_w).  A k-step is 16 staged columns [16 s, 16 s + 16), s = 0..8; it contributes to the two
+// 16-column output blocks s-1 and s, so there is one MMA (M = 128 rows, N = 32, K = 16) per (row tap i, k-step s),
+// against the 32 x 16 Toeplitz slice of row tap i, element (n', kk) = w[i][kk + 16 - n' - a_off] (the same for
+// every s).  The first and last k-step touch one block only (N = 16, half of the slice).  For i = 0 the even
+// k-steps go first with accumulate = 0 (they touch every block exactly once), then the odd ones.
+// Measured: at M = 128 a tcgen05.mma costs ~44 cycles for any N <= 64 (operand fetch), and about twice that
+// when its 8-row x 16-byte core matrices straddle 128-byte lines, so the schedule minimises the MMA count and
+// the layout keeps every core matrix aligned:
+//
+// Layout of the repacked tile (no swizzle, K-major).  MMA row m = 8 g + t stands for tile row g + 16 t, so core
+// matrix g of a k chunk holds staged rows {g + 16 t : t = 0..7} - and the rows a row tap i needs, g + i + 16 t,
+// are simply core matrix g + i.  A k chunk (8 staged columns) is 16 + R-1 core matrices of 128 bytes (rows whose
+// index mod 16 is below R-1 are stored twice); a row tap is a 128-byte offset of the descriptor's start address.
+#include <cstdlib>
+
+#include "kernels.cuh"
+#include "tc05.cuh"
+
+namespace mta {
+
+int make_tensor_map_chunked(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
+                            uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_rows, uint32_t box_chunks);
+
+namespace {
+using namespace tc05;
+
+// Per-role cycle counters of CTA 0 (where each role waits and works), compiled in only with -DMTA_CONV_PROFILE and
+// printed by the launcher when the environment variable MTA_CONV_PROFILE is set.
+#ifdef MTA_CONV_PROFILE
+__device__ long long g_prof[32];
+#define PROF_START long long prof_t = clock64();
+#define PROF_ACC(slot, cond)                                                   \
+    {                                                                          \
+        const long long prof_n = clock64();                                    \
+        if (blockIdx.x == 0 && lane == 0 && (cond)) g_prof[slot] += prof_n - prof_t; \
+        prof_t = prof_n;                                                       \
+    }
+#else
+#define PROF_START
+#define PROF_ACC(slot, cond)
+#endif
+
+constexpr int TM = 128;            // output rows per tile = MMA M
+constexpr int TN = 128;            // output columns per tile
+constexpr int NB = TN / 16;        // 16-column blocks
+constexpr int NKS = 9;             // k-steps of 16 staged columns: 8 (left halo) + 128 + 8
+constexpr int NCH = 2 * NKS;       // staged 8-column chunks
+constexpr int RAWC = 152;          // columns of the row-major staging tile (pitch 304 B = 19 x 16: conflict-free repack)
+constexpr int NRAW = 2;            // stages of the row-major ring
+constexpr int NPK = 2;             // stages of the repacked ring
+constexpr int OUT_BYTES = 2 * TM * 128;   // output staging: two 64-column boxes of 128 rows x 128 bytes, 128-byte swizzle
+constexpr int THREADS = 320;
+
+template <typename T> struct AbFmt;
+template <> struct AbFmt<__nv_bfloat16> { static constexpr int value = 1; };
+template <> struct AbFmt<__half> { static constexpr int value = 0; };
+
+template <typename T> __device__ __forceinline__ uint32_t pack2c(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2c<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t pack2c<__half>(float lo, float hi) {
+    __half2 r = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Matrix descriptor without swizzle: lbo = bytes between the two 8-element k chunks of one MMA, sbo = bytes
+// between groups of 8 rows.
+__device__ __forceinline__ uint64_t smem_desc_plain(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+struct ConvGeom {
+    int C, W, R, S, causal, row_begin, row_end, tiles_n, tiles_m, x_row0, write_upper, split_w;
+    long tiles_per_plane, total_tiles;
+};
+
+// Key tiles that query tile tm reaches.
+__device__ __forceinline__ int conv_key_tiles(const ConvGeom& g, int tm) {
+    if (!g.causal) return g.tiles_n;
+    const int q_last = min(g.row_begin + (tm + 1) * TM, g.row_end);
+    return min((q_last + TN - 1) / TN, g.tiles_n);
+}
+
+// Walks consecutive tile indices without re-deriving (plane, row tile, column tile) from scratch.
+struct TileIter {
+    int plane, tm, tn, nk;
+    __device__ void init(const ConvGeom& g, long t) {
+        plane = (int)(t / g.tiles_per_plane);
+        int r = (int)(t - (long)plane * g.tiles_per_plane);
+        for (tm = 0;; ++tm) {
+            nk = conv_key_tiles(g, tm);
+            if (r < nk) break;
+            r -= nk;
+        }
+        tn = r;
+    }
+    __device__ void next(const ConvGeom& g, int tiles_m) {
+        if (++tn == nk) {
+            tn = 0;
+            if (++tm == tiles_m) { tm = 0; ++plane; }
+            nk = conv_key_tiles(g, tm);
+        }
+    }
+    __device__ int m0(const ConvGeom& g) const { return g.row_begin + tm * TM; }
+    __device__ int n0() const { return tn * TN; }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my,
+                   const void* __restrict__ w, int w_dtype, int y_row0, ConvGeom g, int* err_flag) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t raw_full[NRAW], raw_empty[NRAW], pk_ready[NPK], pk_empty[NPK], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const int R = g.R, S = g.S;
+    const int TH = TM + R - 1;
+    const int NMAT = 16 + R - 1;                               // core matrices per k chunk
+    const int raw_bytes = (TH * RAWC * 2 + 127) & ~127;
+    const int xa_bytes = NCH * NMAT * 128;
+    const int tb_bytes = R * 1024 * (g.split_w ? 2 : 1);      // Toeplitz slices: 32 x 16 per row tap
+    const int pk_bytes = xa_bytes + tb_bytes;
+    uint8_t* out_base = smem;                                  // 1024-byte aligned, as the swizzled TMA store needs
+    uint8_t* raw_base = smem + OUT_BYTES;
+    uint8_t* pk_base = raw_base + NRAW * raw_bytes;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pad_w = (S - 1) / 2;
+    const int pad8 = (pad_w + 7) & ~7;
+    const int a_off = pad8 - pad_w;
+
+    // contiguous range of tiles for this CTA
+    const long per = (g.total_tiles + gridDim.x - 1) / gridDim.x;
+    const long t_begin = (long)blockIdx.x * per;
+    const long t_end = min(t_begin + per, g.total_tiles);
+    const int my_tiles = t_end > t_begin ? (int)(t_end - t_begin) : 0;
+
+    if (tid == 0) abort_flag = *reinterpret_cast<volatile int*>(err_flag);
+    __syncthreads();
+    if (abort_flag != 0 || my_tiles == 0) return;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < NRAW; ++i) {
+                mbar_init(&raw_full[i], 1);
+                mbar_init(&raw_empty[i], 4);
+            }
+            for (int i = 0; i < NPK; ++i) {
+                mbar_init(&pk_ready[i], 4);
+                mbar_init(&pk_empty[i], 1);
+            }
+            for (int i = 0; i < 2; ++i) {
+                mbar_init(&acc_full[i], 1);
+                mbar_init(&acc_empty[i], 4);
+            }
+            fence_mbar_init();
+            prefetch_tensormap(&mx);
+            prefetch_tensormap(&my);
+        }
+        __syncwarp();
+        tmem_alloc(&tmem_slot, 2 * TN);
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            TileIter it;
+            it.init(g, t_begin);
+            for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
+                const int st = n % NRAW;
+                PROF_START
+                mbar_wait(&raw_empty[st], ((n / NRAW) & 1) ^ 1, err_flag);
+                PROF_ACC(0, true)
+                mbar_expect_tx(&raw_full[st], (uint32_t)(TH * RAWC * 2));
+                tma_load_3d(raw_base + st * raw_bytes, &mx, &raw_full[st], it.n0() - pad8, it.m0(g) - (R - 1) - g.x_row0, it.plane);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        constexpr uint32_t idesc32 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 32);
+        constexpr uint32_t idesc16 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 16);
+        const uint32_t lbo_a = (uint32_t)(NMAT * 128);
+        for (int n = 0; n < my_tiles; ++n) {
+            const int pk = n % NPK, ab = n & 1;
+            PROF_START
+            mbar_wait(&pk_ready[pk], (n / NPK) & 1, err_flag);
+            PROF_ACC(1, true)
+            mbar_wait(&acc_empty[ab], ((n >> 1) & 1) ^ 1, err_flag);
+            PROF_ACC(2, true)
+            fence_after_sync();
+            if (lane == 0) {
+                const uint32_t xa_addr = smem_u32(pk_base + pk * pk_bytes), tb_addr = xa_addr + (uint32_t)xa_bytes;
+                const uint32_t d0 = tmem + (uint32_t)(ab * TN);
+                const uint64_t da0 = smem_desc_plain(xa_addr, lbo_a, 128);
+                for (int i = 0; i < R; ++i) {
+                    // Toeplitz slice of row tap i: 32 rows (n') x 16 (kk); k chunks 512 bytes apart, 8-row groups 128 bytes apart
+                    const uint64_t db32 = smem_desc_plain(tb_addr + (uint32_t)(i * 1024), 512, 128);
+                    const uint64_t db_up = db32 + 16;            // rows 16..31: +256 bytes
+                    const uint64_t dl32 = db32 + (uint64_t)(R * 64);
+                    const uint64_t dl_up = dl32 + 16;
+                    const uint64_t da_i = da0 + (uint64_t)(i * 8);   // row tap: +128 bytes
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+                        for (int s = pass; s < NKS; s += 2) {      // even k-steps first: for i = 0 they initialise every block
+                            const uint64_t da = da_i + (uint64_t)(2 * s) * (uint64_t)(NMAT * 8);
+                            const uint32_t acc = (i > 0 || pass > 0) ? 1u : 0u;
+                            if (s == 0) {                           // touches block 0 only: upper half of the slice
+                                mma_f16_ss(d0, da, db_up, idesc16, acc);
+                                if (g.split_w) mma_f16_ss(d0, da, dl_up, idesc16, 1u);
+                            } else if (s == NKS - 1) {              // touches block 7 only: lower half of the slice
+                                mma_f16_ss(d0 + 16u * (NB - 1), da, db32, idesc16, acc);
+                                if (g.split_w) mma_f16_ss(d0 + 16u * (NB - 1), da, dl32, idesc16, 1u);
+                            } else {
+                                mma_f16_ss(d0 + 16u * (s - 1), da, db32, idesc32, acc);
+                                if (g.split_w) mma_f16_ss(d0 + 16u * (s - 1), da, dl32, idesc32, 1u);
+                            }
+                        }
+                    }
+                }
+                mma_commit(&pk_empty[pk]);
+                mma_commit(&acc_full[ab]);
+            }
+            __syncwarp();
+            PROF_ACC(3, true)
+        }
+    } else if (warp < 6) {
+        // ---------------- repack (+ causal zeroing) and Toeplitz slices ----------------
+        const int ft = tid - 64;          // 0..127
+        // Thread ft moves staged row sr = c + 16 t with t = ft % 8, c = (ft / 8 + ft % 8) % 16: eight consecutive lanes
+        // read rows 17 (or 1) apart and write the eight rows of different core matrices - no bank conflicts either way.
+        const int rt = ft & 7, rc = ((ft >> 3) + rt) & 15;
+        TileIter it;
+        it.init(g, t_begin);
+        int prev_head[NPK];
+#pragma unroll
+        for (int i = 0; i < NPK; ++i) prev_head[i] = -1;
+        for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
+            const int st = n % NRAW, pk = n % NPK;
+            const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
+            const int head = plane % g.C;
+            const uint8_t* raw = raw_base + st * raw_bytes;
+            uint8_t* xa = pk_base + pk * pk_bytes;
+            uint8_t* tb = xa + xa_bytes;
+            // the repacked stage (and its Toeplitz slices) is free once the MMAs of tile n - NPK are done
+            PROF_START
+            mbar_wait(&pk_empty[pk], ((n / NPK) & 1) ^ 1, err_flag);
+            PROF_ACC(4, warp == 2)
+            const int ph = (pk == 0) ? prev_head[0] : prev_head[1];
+            if (pk == 0) prev_head[0] = head; else prev_head[1] = head;
+            if (ph != head) {
+                const int total = R * 512;
+                for (int idx = ft; idx < total; idx += 128) {
+                    const int i = idx / 512, e = idx % 512;
+                    const int nn = e / 16, kk = e % 16;
+                    const int j = kk + 16 - nn - a_off;
+                    const float wv = (j >= 0 && j < S) ? load_weight(w, ((long)head * R + i) * S + j, w_dtype) : 0.0f;
+                    const T hi = from_f32<T>(wv);
+                    const int off = i * 1024 + (kk / 8) * 512 + (nn / 8) * 128 + (nn % 8) * 16 + (kk % 8) * 2;
+                    *reinterpret_cast<T*>(tb + off) = hi;
+                    if (g.split_w) *reinterpret_cast<T*>(tb + R * 1024 + off) = from_f32<T>(wv - to_f32<T>(hi));
+                }
+            }
+            PROF_ACC(5, warp == 2)
+            mbar_wait(&raw_full[st], (n / NRAW) & 1, err_flag);
+            PROF_ACC(6, warp == 2)
+            // staged row sr is query m0-(R-1)+sr; chunk ch holds keys n0-pad8+8ch .. +7
+            const bool diag = g.causal && n0 - pad8 + NCH * 8 - 1 > m0 - (R - 1);
+#pragma unroll 1
+            for (int pass = 0; pass < 2; ++pass) {
+                // pass 0: rows 0..127 at (matrix sr%16, slot sr/16) and, when sr >= 16 and sr%16 < R-1, again at
+                // (matrix 16 + sr%16, slot sr/16 - 1); pass 1: rows 128..TH-1, which only have the second position
+                int sr, off0, off1;
+                if (pass == 0) {
+                    sr = rc + 16 * rt;
+                    off0 = (rc * 8 + rt) * 16;
+                    off1 = (rt >= 1 && rc < R - 1) ? ((16 + rc) * 8 + rt - 1) * 16 : -1;
+                } else {
+                    if (ft >= R - 1) break;
+                    sr = 128 + ft;
+                    off0 = ((16 + ft) * 8 + 7) * 16;
+                    off1 = -1;
+                }
+                const uint8_t* src = raw + sr * (RAWC * 2);
+                const int qq = m0 - (R - 1) + sr;
+#pragma unroll 6
+                for (int ch = 0; ch < NCH; ++ch) {
+                    uint4 v = *reinterpret_cast<const uint4*>(src + ch * 16);
+                    if (diag) {
+                        const int kfirst = n0 - pad8 + ch * 8;
+                        if (kfirst > qq) {
+                            v = make_uint4(0u, 0u, 0u, 0u);
+                        } else if (kfirst + 7 > qq) {
+                            uint16_t* e16 = reinterpret_cast<uint16_t*>(&v);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (kfirst + e > qq) e16[e] = 0;
+                        }
+                    }
+                    uint8_t* dch = xa + ch * NMAT * 128;
+                    *reinterpret_cast<uint4*>(dch + off0) = v;
+                    if (off1 >= 0) *reinterpret_cast<uint4*>(dch + off1) = v;
+                }
+            }
+            fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&raw_empty[st]);
+                mbar_arrive(&pk_ready[pk]);
+            }
+            PROF_ACC(7, warp == 2)
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;
+        const bool issuer = (warp == 6 && lane == 0);
+        const int mrow = quarter * 32 + lane;                // accumulator row (TMEM lane) this thread owns ...
+        const int row = (mrow >> 3) + 16 * (mrow & 7);       // ... which is this row of the tile
+        uint8_t* orow = out_base + row * 128;
+        TileIter it;
+        it.init(g, t_begin);
+        for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
+            const int ab = n & 1;
+            const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
+            PROF_START
+            mbar_wait(&acc_full[ab], (n >> 1) & 1, err_flag);
+            __syncwarp();
+            fence_after_sync();
+            PROF_ACC(8, warp == 6)
+            if (issuer) bulk_wait_read();                    // the previous tile's store has finished reading the staging tile
+            named_barrier(1, 128);
+            PROF_ACC(9, warp == 6)
+            const int q = m0 + row;
+#pragma unroll 1
+            for (int cblk = 0; cblk < TN / 32; ++cblk) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TN + cblk * 32), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int v8 = 0; v8 < 4; ++v8) {
+                    const int col = cblk * 32 + v8 * 8;
+                    const int k = n0 + col;
+                    float f[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v8 * 8 + e]);
+                    if (g.causal && k + 7 > q) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (k + e > q) f[e] = 0.0f;          // entries above the diagonal inside the tile are written as 0
+                    }
+                    uint4 o;
+                    o.x = pack2c<T>(f[0], f[1]);
+                    o.y = pack2c<T>(f[2], f[3]);
+                    o.z = pack2c<T>(f[4], f[5]);
+                    o.w = pack2c<T>(f[6], f[7]);
+                    const int c = (col & 63) >> 3;
+                    *reinterpret_cast<uint4*>(orow + (col >> 6) * (TM * 128) + ((c ^ (row & 7)) << 4)) = o;
+                }
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            PROF_ACC(10, warp == 6)
+            fence_proxy_async();                             // staging tile written through the generic proxy, read by TMA
+            named_barrier(1, 128);
+            if (issuer) {
+                // rows past row_end and columns past W are clipped by the tensor map
+                tma_store_3d(&my, out_base, n0, m0 - y_row0, plane);
+                if (n0 + 64 < g.W) tma_store_3d(&my, out_base + TM * 128, n0 + 64, m0 - y_row0, plane);
+                bulk_commit();
+            }
+            PROF_ACC(11, warp == 6)
+        }
+        if (issuer) bulk_wait_all();
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 2 * TN);
+}
+
+// Zero fill of the key tiles that lie entirely above the diagonal (what the conv kernel never visits).
+template <typename T>
+__global__ void __launch_bounds__(256)
+fill_above_kernel(T* __restrict__ y, PlaneView yv, int W, int row_begin, int row_end) {
+    const long plane = blockIdx.y;
+    const int q = row_begin + (int)blockIdx.x;
+    if (q >= row_end) return;
+    const int tm = (q - row_begin) / TM;
+    const int q_last = min(row_begin + (tm + 1) * TM, row_end);
+    const int k_start = min(((q_last + TN - 1) / TN) * TN, W);      // first key the conv tiles of this row do not cover
+    uint4* row = reinterpret_cast<uint4*>(y + plane * yv.plane_stride + (long)(q - yv.row0) * yv.width);
+    for (int ch = k_start / 8 + threadIdx.x; ch < W / 8; ch += 256) row[ch] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+size_t conv2d_tc05_smem_bytes(int R, bool split_w) {
+    const int TH = TM + R - 1;
+    return (size_t)1024 + OUT_BYTES + (size_t)NRAW * ((TH * RAWC * 2 + 127) & ~127) +
+           (size_t)NPK * ((size_t)NCH * (16 + R - 1) * 128 + (size_t)R * 1024 * (split_w ? 2 : 1));
+}
+
+template <typename T>
+int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
+                long planes, int C, int W, int R, int S, int causal, int row_begin, int row_end, bool write_upper,
+                cudaStream_t st) {
+    CUtensorMap mx;
+    int rc;
+    const int TH = TM + R - 1;
+    if ((rc = make_tensor_map_3d(&mx, x, (uint64_t)planes, (uint64_t)x_rows_stored, (uint64_t)W, (uint64_t)xv.width,
+                                 (uint64_t)xv.plane_stride, RAWC, (uint32_t)TH, false)))
+        return rc;
+    int* flag = nullptr;
+    if ((rc = wait_flag_ptr(&flag))) return rc;
+    CUtensorMap my;      // rows past row_end are outside this map, so a tile's store never touches them
+    if ((rc = make_tensor_map_3d(&my, y, (uint64_t)planes, (uint64_t)(row_end - yv.row0), (uint64_t)W, (uint64_t)yv.width,
+                                 (uint64_t)yv.plane_stride, 64, TM, true)))
+        return rc;
+    ConvGeom g;
+    g.C = C; g.W = W; g.R = R; g.S = S; g.causal = causal; g.row_begin = row_begin; g.row_end = row_end;
+    g.tiles_n = (W + TN - 1) / TN; g.x_row0 = xv.row0; g.write_upper = write_upper ? 1 : 0;
+    g.split_w = w_dtype == MTA_F32 ? 1 : 0;
+    const int tiles_m = (row_end - row_begin + TM - 1) / TM;
+    g.tiles_m = tiles_m;
+    long per_plane = 0;
+    for (int tm = 0; tm < tiles_m; ++tm) {
+        const int q_last = std::min(row_begin + (tm + 1) * TM, row_end);
+        per_plane += causal ? std::min((q_last + TN - 1) / TN, g.tiles_n) : g.tiles_n;
+    }
+    g.tiles_per_plane = per_plane;
+    g.total_tiles = per_plane * planes;
+    int dev = 0, sms = 0;
+    MTA_CUDA_OK(cudaGetDevice(&dev));
+    MTA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const size_t smem = conv2d_tc05_smem_bytes(R, g.split_w != 0);
+    MTA_REQUIRE(smem <= 227 * 1024, "conv2d (tcgen05): kernel with %d row taps needs %zu bytes of shared memory", R, smem);
+    MTA_CUDA_OK(cudaFuncSetAttribute(conv2d_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const unsigned grid = (unsigned)std::min<long>(g.total_tiles, sms);
+    conv2d_tc05_kernel<T><<<grid, THREADS, smem, st>>>(mx, my, w, w_dtype, yv.row0, g, flag);
+    MTA_LAUNCH_OK("conv2d_tc05_kernel");
+#ifdef MTA_CONV_PROFILE
+    if (getenv("MTA_CONV_PROFILE")) {
+        cudaDeviceSynchronize();
+        long long h[32], z[32] = {};
+        cudaMemcpyFromSymbol(h, g_prof, sizeof(h));
+        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
+        const long n0 = (g.total_tiles + grid - 1) / grid;
+        fprintf(stderr, "conv2d_tc05 clk/tile (CTA 0, %ld tiles): producer wait_empty %lld | mma wait_ready %lld wait_acc %lld issue %lld | "
+                "repack wait_free %lld toeplitz %lld wait_raw %lld move %lld | epilogue wait_acc %lld wait_store %lld drain %lld store %lld\n",
+                n0, h[0] / n0, h[1] / n0, h[2] / n0, h[3] / n0, h[4] / n0, h[5] / n0, h[6] / n0, h[7] / n0, h[8] / n0, h[9] / n0,
+                h[10] / n0, h[11] / n0);
+    }
+#endif
+    if (causal && write_upper && W > TN) {
+        dim3 fgrid((unsigned)(row_end - row_begin), (unsigned)planes);
+        fill_above_kernel<T><<<fgrid, 256, 0, st>>>(static_cast<T*>(y), yv, W, row_begin, row_end);
+        MTA_LAUNCH_OK("fill_above_kernel");
+    }
+    return MTA_OK;
+}
+
+}  // namespace
+
+
+bool conv2d_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int W, int R, int S, int dtype,
+                           int w_dtype) {
+    return dtype != MTA_F32 && S <= 17 && conv2d_tc05_smem_bytes(R, w_dtype == MTA_F32) <= 227 * 1024 && W % 8 == 0 && xv.width == W && yv.width == W &&
+           xv.plane_stride % 8 == 0 && yv.plane_stride % 8 == 0 && aligned16(x) && aligned16(y);
+}
+
+int conv2d_tc05_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
+                       long planes, int C, int H, int W, int R, int S, int causal, int row_begin, int row_end,
+                       bool write_upper, int dtype, cudaStream_t st) {
+    (void)H;
+    if (dtype == MTA_BF16)
+        return launch_tc05<__nv_bfloat16>(x, xv, x_rows_stored, w, w_dtype, y, yv, planes, C, W, R, S, causal, row_begin,
+                                          row_end, write_upper, st);
+    return launch_tc05<__half>(x, xv, x_rows_stored, w, w_dtype, y, yv, planes, C, W, R, S, causal, row_begin, row_end,
+                               write_upper, st);
+}
+
+}  // namespace mta

@@ -74,6 +74,33 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint
     return MTA_OK;
 }
 
+// 4-D map (8 columns, rows, 8-column chunks, planes) of a [planes][rows][cols] tensor of 16-bit elements: a box
+// {8, box_rows, box_chunks, 1} lands in shared memory as [chunk][row][8 columns], the layout a tcgen05 matrix
+// descriptor without swizzle reads with any row offset.  Out-of-range rows and chunks read as zero.
+int make_tensor_map_chunked(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
+                            uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_rows, uint32_t box_chunks) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return MTA_ERR_CUDA;
+    }
+    MTA_REQUIRE(aligned16(base) && cols % 8 == 0 && (row_pitch_elems * 2) % 16 == 0 && (plane_pitch_elems * 2) % 16 == 0 &&
+                    box_rows <= 256 && box_chunks <= 256,
+                "chunked tensor map: unsupported geometry");
+    cuuint64_t dims[4] = {8, rows, cols / 8, planes};
+    cuuint64_t strides[3] = {row_pitch_elems * 2, 16, plane_pitch_elems * 2};
+    cuuint32_t box[4] = {8, box_rows, box_chunks, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (chunked view) failed with CUresult %d", (int)r);
+        return MTA_ERR_CUDA;
+    }
+    return MTA_OK;
+}
+
 namespace {
 using namespace tc05;
 

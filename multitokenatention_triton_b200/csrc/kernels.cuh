@@ -42,6 +42,14 @@ int qk_scores_simt_launch(const void* q, const void* k, void* s, PlaneView sv, i
 int pv_simt_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
                    int row_begin, int row_end, int dtype, cudaStream_t st);
 
+// tcgen05 version of the conv (conv2d_tc05.cu): 16-bit dtypes, S <= 17, W a multiple of 8, R small enough for its
+// shared-memory rings (R <= 13 with 16-bit weights).
+bool conv2d_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int W, int R, int S, int dtype,
+                           int w_dtype);
+int conv2d_tc05_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
+                       long planes, int C, int H, int W, int R, int S, int causal, int row_begin, int row_end,
+                       bool write_upper, int dtype, cudaStream_t st);
+
 // tcgen05 tensor-core versions (gemm_tc05.cu): 16-bit dtypes, D in {64,128}, S a multiple of 8.
 bool tc05_contractions_supported(int S, int D, int dtype, const void* a, const void* b, const void* c, PlaneView view);
 int qk_scores_tc05_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,

@@ -86,9 +86,130 @@ softmax_rows_kernel(const T* __restrict__ x, PlaneView xv, T* __restrict__ y, Pl
         for (int k = n + tid; k < Q; k += SM_THREADS) yr[k] = from_f32<T>(0.0f);
 }
 
+// Vector version for 16-bit dtypes with 16-byte aligned rows: a CTA of 128 threads owns one row and keeps it
+// in registers as NCH chunks of 8 keys per thread (rows of up to NCH*1024 keys), so the row is read once with
+// 16-byte loads and written once with 16-byte stores.
+constexpr int VT = 128;
+
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]);
+template <> __device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <> __device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2s(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2s<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t pack2s<__half>(float lo, float hi) {
+    __half2 r = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+template <typename T, int NCH>
+__global__ void __launch_bounds__(VT)
+softmax_rows_vec_kernel(const T* __restrict__ x, PlaneView xv, T* __restrict__ y, PlaneView yv, int Q, int causal,
+                        int row_begin, int write_upper, float pre_scale, int round_prescaled) {
+    __shared__ float red[2][VT / 32];
+    const int p = row_begin + blockIdx.x;
+    const long plane = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = causal ? min(p + 1, Q) : Q;
+    const int nch = (n + 7) >> 3;                       // chunks that hold at least one valid key
+    const uint4* xr = reinterpret_cast<const uint4*>(x + xv.at(plane, p, 0));
+    uint4* yr = reinterpret_cast<uint4*>(y + yv.at(plane, p, 0));
+    float v[NCH][8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int ch = tid + c * VT;
+        if (ch < nch) {
+            unpack8<T>(__ldg(xr + ch), v[c]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float t = v[c][e] * pre_scale;
+                if (round_prescaled) t = round_to<T>(t);
+                if (ch * 8 + e >= n) t = -INFINITY;     // keys past the diagonal inside the last chunk
+                v[c][e] = t;
+                mx = fmaxf(mx, t);
+            }
+        }
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[0][warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0][0], red[0][1]), fmaxf(red[0][2], red[0][3]));
+    float sum = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        if (tid + c * VT < nch) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float ex = __expf(v[c][e] - mx);   // exp(-inf) = 0 for the masked tail
+                v[c][e] = ex;
+                sum += ex;
+            }
+        }
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[1][warp] = sum;
+    __syncthreads();
+    const float inv = 1.0f / (red[1][0] + red[1][1] + red[1][2] + red[1][3]);
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int ch = tid + c * VT;
+        if (ch < nch) {
+            uint4 o;
+            o.x = pack2s<T>(v[c][0] * inv, v[c][1] * inv);
+            o.y = pack2s<T>(v[c][2] * inv, v[c][3] * inv);
+            o.z = pack2s<T>(v[c][4] * inv, v[c][5] * inv);
+            o.w = pack2s<T>(v[c][6] * inv, v[c][7] * inv);
+            if (!write_upper && ch * 8 + 8 > n) {       // last chunk: keys past the diagonal stay untouched
+                T* dst = reinterpret_cast<T*>(yr + ch);
+                const T* src = reinterpret_cast<const T*>(&o);
+                for (int e = 0; e < 8; ++e)
+                    if (ch * 8 + e < n) dst[e] = src[e];
+            } else {
+                yr[ch] = o;
+            }
+        }
+    }
+    if (write_upper)
+        for (int ch = nch + tid; ch < (Q >> 3); ch += VT) yr[ch] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+template <typename T, int NCH>
+int launch_vec(const void* x, PlaneView xv, void* y, PlaneView yv, long planes, int Q, int causal, int row_begin,
+               int row_end, bool write_upper, float pre_scale, int round_prescaled, cudaStream_t st) {
+    dim3 grid((unsigned)(row_end - row_begin), (unsigned)planes);
+    softmax_rows_vec_kernel<T, NCH><<<grid, VT, 0, st>>>(static_cast<const T*>(x), xv, static_cast<T*>(y), yv, Q, causal,
+                                                        row_begin, write_upper ? 1 : 0, pre_scale, round_prescaled);
+    MTA_LAUNCH_OK("softmax_rows_vec_kernel");
+    return MTA_OK;
+}
+
 template <typename T>
 int launch(const void* x, PlaneView xv, void* y, PlaneView yv, long planes, int Q, int causal, int row_begin,
            int row_end, bool write_upper, float pre_scale, int round_prescaled, cudaStream_t st) {
+    if constexpr (sizeof(T) == 2) if (Q % 8 == 0 && Q <= 16 * 8 * VT && xv.plane_stride % 8 == 0 && yv.plane_stride % 8 == 0 &&
+        xv.width % 8 == 0 && yv.width % 8 == 0 && aligned16(x) && aligned16(y)) {
+        const int longest = causal ? (row_end < Q ? row_end : Q) : Q;
+        const int need = (longest + 8 * VT - 1) / (8 * VT);
+        if (need <= 1) return launch_vec<T, 1>(x, xv, y, yv, planes, Q, causal, row_begin, row_end, write_upper, pre_scale, round_prescaled, st);
+        if (need <= 2) return launch_vec<T, 2>(x, xv, y, yv, planes, Q, causal, row_begin, row_end, write_upper, pre_scale, round_prescaled, st);
+        if (need <= 4) return launch_vec<T, 4>(x, xv, y, yv, planes, Q, causal, row_begin, row_end, write_upper, pre_scale, round_prescaled, st);
+        if (need <= 8) return launch_vec<T, 8>(x, xv, y, yv, planes, Q, causal, row_begin, row_end, write_upper, pre_scale, round_prescaled, st);
+        return launch_vec<T, 16>(x, xv, y, yv, planes, Q, causal, row_begin, row_end, write_upper, pre_scale, round_prescaled, st);
+    }
     const int cache = Q < ROW_CACHE ? Q : ROW_CACHE;
     const size_t smem = (size_t)cache * sizeof(float);
     if (smem > 48 * 1024)

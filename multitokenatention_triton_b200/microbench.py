@@ -1,0 +1,129 @@
+"""Micro-benchmarks of the stand-alone kernels on the configurations their roofline targets are quoted on.
+
+    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|qk|pv|all] [--variant V]
+                                                        [--batch N] [--seq S] [--iters K]
+
+  conv2d       causal depthwise conv 6x11 on a (B=4, H=16, S=2048, S) bf16 score plane
+  head_linear  16x16 head mix on post-softmax probabilities of the same shape
+
+Each kernel is timed alone with CUDA events on the launching stream (3 warm-up launches, then K timed ones;
+input + output of one launch exceed the 126 MB L2).  One JSON line per kernel:
+algorithmic bytes = read the lower triangle once + write the whole output (zero / fill included), divided by
+the mean launch time, against the measured copy bandwidth in MEASURED_PEAKS.json when present.
+--variant selects 0 auto, 1 CUDA-core, 2 tensor-core (see mta_set_variant).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import _lib, ops
+from .synthetic import make_conv_inputs, make_head_linear_inputs
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    e.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def _line(name, ms, nbytes=None, flops=None, **extra):
+    hbm, tf, kind = _peaks()
+    out = {"kernel": name, "ms": ms, "peak_kind": kind}
+    if nbytes is not None:
+        out.update(bound="hbm", bytes_algorithmic=nbytes, achieved=nbytes / ms / 1e6, peak=hbm, unit="GB/s",
+                   frac=nbytes / ms / 1e6 / hbm, frac_of_nominal_8000=nbytes / ms / 1e6 / 8000.0)
+    else:
+        out.update(bound="tensor", flops_algorithmic=flops, achieved=flops / ms / 1e9, peak=tf, unit="TFLOP/s",
+                   frac=flops / ms / 1e9 / tf, frac_of_nominal_2250=flops / ms / 1e9 / 2250.0)
+    out.update(extra)
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "qk", "pv", "all"])
+    ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--dim", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"])
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    dtype = getattr(torch, a.dtype)
+    es = torch.empty(0, dtype=dtype).element_size()
+    N, C, S, D = a.batch, a.heads, a.seq, a.dim
+    tri = S * (S + 1) // 2
+    shape = f"B{N} H{C} S{S} {a.dtype}"
+    for key in ("conv2d", "head_linear", "gemm"):
+        _lib.set_variant(key, a.variant)
+
+    if a.which in ("conv2d", "all"):
+        inp = make_conv_inputs(N, C, S, D, 6, 11, dtype, seed=1)
+        x, w = inp["x"].to(dev), inp["w"].to(dev)
+        y = torch.empty_like(x)
+
+        def run():
+            _lib.check(_lib.lib().mta_conv2d_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, C, S, S, 6, 11, 1,
+                                                 _lib.dtype_code(x), _lib.dtype_code(w), _lib.stream_ptr(dev)), "conv2d")
+        ms = _time(run, a.iters)
+        _line("conv2d 6x11 causal", ms, nbytes=es * N * C * (tri + S * S), shape=shape, variant=a.variant,
+              lower_only_bytes=2 * es * N * C * tri)
+        del x, y
+    if a.which in ("head_linear", "softmax", "all"):
+        inp = make_head_linear_inputs(N, C, S, dtype, seed=2)
+        x, W = inp["x"].to(dev), inp["W"].to(dev)
+        y = torch.empty_like(x)
+        if a.which != "softmax":
+            for fill in (0.0, float("-inf")):
+                def run():
+                    _lib.check(_lib.lib().mta_head_linear_fwd(x.data_ptr(), W.data_ptr(), y.data_ptr(), N, C, S, S, 1, fill,
+                                                              _lib.dtype_code(x), _lib.dtype_code(W), _lib.stream_ptr(dev)),
+                               "head_linear")
+                ms = _time(run, a.iters)
+                _line(f"head_linear {C}x{C} causal fill={fill}", ms, nbytes=es * N * C * (tri + S * S), shape=shape,
+                      variant=a.variant)
+        if a.which in ("softmax", "all"):
+            ms = _time(lambda: ops.softmax_fwd(x, True, out=y), a.iters)
+            _line("softmax causal rows", ms, nbytes=es * N * C * (tri + S * S), shape=shape)
+        del x, y
+    if a.which in ("qk", "pv", "all"):
+        g = torch.Generator().manual_seed(3)
+        q, k, v = (torch.randn(N, C, S, D, generator=g).to(dtype).to(dev) for _ in range(3))
+        s = torch.zeros(N, C, S, S, dtype=dtype, device=dev)
+        if a.which in ("qk", "all"):
+            ms = _time(lambda: ops.qk_scores_fwd(q, k, D ** -0.5, True, out=s), a.iters)
+            _line("qk_scores causal", ms, flops=2.0 * D * N * C * tri, shape=shape + f" D{D}", variant=a.variant,
+                  write_gbs=es * N * C * tri / ms / 1e6)
+        if a.which in ("pv", "all"):
+            ms = _time(lambda: ops.pv_fwd(s, v, True), a.iters)
+            _line("pv causal", ms, flops=2.0 * D * N * C * tri, shape=shape + f" D{D}", variant=a.variant,
+                  read_gbs=es * N * C * tri / ms / 1e6)
+    _lib.device_status()
+
+
+if __name__ == "__main__":
+    main()

@@ -34,12 +34,12 @@ def conv_mma_able(dtype, S, Sk):
     return dtype != torch.float32 and Sk <= 17 and S % 8 == 0
 
 
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("name", list(CONV_CASES))
 def test_conv2d(name, variant, golden):
-    """variant 1 = CUDA-core kernel, 2 = tensor-core (Toeplitz MMA + TMA) kernel."""
+    """variant 1 = CUDA-core kernel, 2 = mma.sync Toeplitz kernel, 3 = tcgen05 Toeplitz kernel."""
     N, C, S, D, R, Sk, dtype, seed, causal = CONV_CASES[name]
-    if variant == 2 and not conv_mma_able(dtype, S, Sk):
+    if variant >= 2 and not conv_mma_able(dtype, S, Sk):
         pytest.skip("outside the tensor-core kernel's domain")
     inp = make_conv_inputs(N, C, S, D, R, Sk, dtype, seed)          # upper triangle left as computed
     m = Conv2dTriton(C, (R, Sk), causal=causal).to(DEV).to(dtype)
@@ -71,19 +71,22 @@ def test_conv2d_fp32_weights_and_odd_shapes(S, R, Sk, dtype):
     one_stage_close(npf(y), ref, dtype, f"S={S} {R}x{Sk}")
 
 
+@pytest.mark.parametrize("variant", [2, 3])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("S,R,Sk,causal", [(512, 6, 11, True), (264, 3, 3, True), (136, 1, 1, True), (320, 11, 15, True),
                                              (200, 2, 17, True), (128, 4, 4, True), (384, 6, 11, False), (8, 3, 3, True)])
-def test_conv2d_tensor_core(S, R, Sk, causal, dtype):
-    """The Toeplitz-MMA kernel on larger planes, with NaN planted above the diagonal (must never be read)."""
+def test_conv2d_tensor_core(S, R, Sk, causal, dtype, variant):
+    """The Toeplitz tensor-core kernels on larger planes, with NaN planted above the diagonal (must never be read)."""
+    if variant == 3 and R > 8:
+        pytest.skip("the tcgen05 kernel's shared-memory rings take fewer row taps")
     inp = make_conv_inputs(2, 3, S, 32, R, Sk, dtype, seed=2000 + S + R)
     x = inp["x"].clone()
     if causal:
         iu = torch.triu_indices(S, S, 1)
         x[..., iu[0], iu[1]] = float("nan")
-    _lib.set_variant("conv2d", 2)
+    _lib.set_variant("conv2d", variant)
     try:
-        y = ops.conv2d_fwd(x.to(DEV), inp["w"].to(DEV), causal)
+        y = ops.conv2d_fwd(x.to(DEV), inp["w"].to(DEV), causal)      # weights in the activation dtype
         _lib.device_status()
     finally:
         _lib.set_variant("conv2d", 0)
