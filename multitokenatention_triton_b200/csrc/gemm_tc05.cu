@@ -135,12 +135,13 @@ __device__ __forceinline__ int key_tiles_for(int tq, int row_begin, int row_end,
 
 // ------------------------------------------------------------------------------------------------
 // One CTA (4 warps) per 128 x 128 score tile.  Thread 0 issues the TMA loads and the MMAs; all four warps
-// drain the accumulator: warp w owns TMEM lanes 32w..32w+31 = tile rows, each lane one row.
+// drain the accumulator: warp w owns TMEM lanes 32w..32w+31 = tile rows, each lane one row.  The tile leaves
+// through shared memory and a TMA tiled store.
 template <typename T, int D>
 __global__ void __launch_bounds__(128)
-qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk, T* __restrict__ s,
-                      PlaneView sv, int S, float scale, int round_scale, int causal, int row_begin, int row_end,
-                      int* err_flag) {
+qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                      const __grid_constant__ CUtensorMap ms, int s_row0, int S, float scale, int round_scale, int causal,
+                      int row_begin, int row_end, int* err_flag) {
     constexpr int NBOX = D / 64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_1024(smem_raw);
@@ -162,7 +163,6 @@ qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     }
     const int bh = (int)blockIdx.y;
     const int q0 = row_begin + tq * TILE, k0 = tk * TILE;
-    const int q_end = min(q0 + TILE, row_end);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (warp == 0) {
@@ -172,6 +172,7 @@ qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
             fence_mbar_init();
             prefetch_tensormap(&mq);
             prefetch_tensormap(&mk);
+            prefetch_tensormap(&ms);
         }
         __syncwarp();
         tmem_alloc(&tmem_slot, 128);
@@ -204,43 +205,47 @@ qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     __syncwarp();
     fence_after_sync();
 
-    const int q = q0 + warp * 32 + lane;
+    // Epilogue: a thread owns one row of the tile, so the 16-bit tile is staged in shared memory (over the operand
+    // tiles, which are dead now) in the 128-byte-swizzled layout and leaves as two TMA tiled stores.
+    const int row = warp * 32 + lane;
+    const int q = q0 + row;
     const float sc = round_scale ? round_to<T>(scale) : scale;
-    T* srow = s + sv.at(bh, q < q_end ? q : q0, 0);
+    uint8_t* orow = smem + row * 128;
 #pragma unroll 1
     for (int c = 0; c < TILE / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
         tmem_ld_wait();
-        if (q >= q_end) continue;
-        const int kbase = k0 + c * 32;
-        const int klim = min(S, causal ? q + 1 : S);          // keys < klim are stored
 #pragma unroll
         for (int v8 = 0; v8 < 4; ++v8) {
-            const int k = kbase + v8 * 8;
-            if (k >= klim) break;
+            const int col = c * 32 + v8 * 8;
+            const int k = k0 + col;
             float f[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float a = __uint_as_float(r[v8 * 8 + e]);
                 f[e] = round_scale ? round_to<T>(a) * sc : a * sc;
+                if (causal && k + e > q) f[e] = 0.0f;        // above the diagonal inside a visited tile: written as 0
             }
-            if (k + 8 <= klim) {
-                uint4 o;
-                o.x = pack2<T>(f[0], f[1]);
-                o.y = pack2<T>(f[2], f[3]);
-                o.z = pack2<T>(f[4], f[5]);
-                o.w = pack2<T>(f[6], f[7]);
-                *reinterpret_cast<uint4*>(srow + k) = o;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    if (k + e < klim) srow[k + e] = from_f32<T>(f[e]);
-            }
+            uint4 o;
+            o.x = pack2<T>(f[0], f[1]);
+            o.y = pack2<T>(f[2], f[3]);
+            o.z = pack2<T>(f[4], f[5]);
+            o.w = pack2<T>(f[6], f[7]);
+            const int ch = (col & 63) >> 3;
+            *reinterpret_cast<uint4*>(orow + (col >> 6) * BOX_BYTES + ((ch ^ (row & 7)) << 4)) = o;
         }
     }
+    fence_proxy_async();
     fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) {
+        // rows past row_end and columns past S are outside the tensor map and are clipped
+        tma_store_3d(&ms, smem, k0, q0 - s_row0, bh);
+        if (k0 + 64 < S) tma_store_3d(&ms, smem + BOX_BYTES, k0 + 64, q0 - s_row0, bh);
+        bulk_commit();
+        bulk_wait_read();
+    }
     if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
@@ -385,6 +390,9 @@ int launch_qk(const void* q, const void* k, void* s, PlaneView sv, int B, int H,
     int rc;
     if ((rc = make_tensor_map_3d(&mq, q, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
     if ((rc = make_tensor_map_3d(&mk, k, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
+    CUtensorMap ms;      // rows past row_end are outside this map, so a tile's store never touches them
+    if ((rc = make_tensor_map_3d(&ms, s, (uint64_t)B * H, (uint64_t)(row_end - sv.row0), S, S, (uint64_t)sv.plane_stride, 64, TILE, true)))
+        return rc;
     int* flag = nullptr;
     if ((rc = wait_flag_ptr(&flag))) return rc;
     const int n_qt = (row_end - row_begin + TILE - 1) / TILE, all_k = (S + TILE - 1) / TILE;
@@ -396,8 +404,8 @@ int launch_qk(const void* q, const void* k, void* s, PlaneView sv, int B, int H,
     const size_t smem = 2 * (D / 64) * BOX_BYTES + 1024;
     MTA_CUDA_OK(cudaFuncSetAttribute(qk_scores_tc05_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)tiles, (unsigned)(B * H));
-    qk_scores_tc05_kernel<T, D><<<grid, 128, smem, st>>>(mq, mk, static_cast<T*>(s), sv, S, scale, round_scale, causal,
-                                                         row_begin, row_end, flag);
+    qk_scores_tc05_kernel<T, D><<<grid, 128, smem, st>>>(mq, mk, ms, sv.row0, S, scale, round_scale, causal, row_begin,
+                                                         row_end, flag);
     MTA_LAUNCH_OK("qk_scores_tc05_kernel");
     return MTA_OK;
 }

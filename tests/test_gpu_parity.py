@@ -259,6 +259,23 @@ def test_mta_forward_row_range(name, rows):
     assert_parity(npf(out[0, :, r0:r1]), ref, wl.dtype, f"{name} rows {rows}")
 
 
+@pytest.mark.parametrize("name,world", [("c1", 4), ("s130_6x11_bf16", 4), ("s192_h32_f16", 2), ("c1", 2)])
+def test_sharded_forward_on_one_gpu(name, world):
+    """Every shard of a plan, run one after the other on this GPU through the row-range entry point, reassembles
+    into the unsharded forward bit for bit (the multi-process gather itself is covered on CPU ranks)."""
+    from multitokenatention_triton_b200 import sharding
+    wl = MTA_CASES[name]
+    inp = make_mta_inputs(wl)
+    d = {k: t.to(DEV) for k, t in inp.items()}
+    weights = [d[n] for n in ("w1", "W1", "w2", "W2")]
+    full = ops.mta_fused_fwd(d["q"], d["k"], d["v"], *weights, True)
+    out = torch.zeros_like(full)
+    for b0, b1, r0, r1 in sharding.plan_shards(wl.B, wl.S, world, row_align=16):
+        loc = sharding.local_forward(d["q"][b0:b1], d["k"][b0:b1], d["v"][b0:b1], weights, (b0, b1, r0, r1))
+        out[b0:b1, :, r0:r1] = loc
+    assert torch.equal(out, full)
+
+
 @pytest.mark.parametrize("name", list(CONV_ATTN_CASES))
 def test_conv_attention(name, golden):
     wl, causal = CONV_ATTN_CASES[name]
