@@ -89,6 +89,19 @@ int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w
                       float scale, int dtype, int w_dtype, void* stream);
 
 /*
+ * mta_conv_attn_fwd without a caller workspace (this entry point has no counterpart in the reference): the two
+ * scratch score planes live in a 64 MiB array built into the library (MTA_STATIC_SCRATCH_BYTES, also returned by
+ * mta_static_scratch_bytes()), for callers that must not or cannot allocate device memory.  Same arguments and
+ * results as mta_conv_attn_fwd; returns 1 with a message when 2*B*H*S*S*elemsize (256-byte rounded per plane)
+ * exceeds the array.  It allocates nothing.  The first call on each device looks up the array's device address
+ * (do it before any stream capture).  All calls share the array: calls that overlap on the GPU race.
+ */
+#define MTA_STATIC_SCRATCH_BYTES ((size_t)64 << 20)
+size_t mta_static_scratch_bytes(void);
+int mta_conv_attn_fwd_static(const void* q, const void* k, const void* v, const void* w, void* o, int B, int H, int S,
+                             int D, int cq, int ck, int causal, float scale, int dtype, int w_dtype, void* stream);
+
+/*
  * Full four-stage MTA forward: QK^T/sqrt(D) -> conv (w1) -> head mix (W1) -> softmax -> conv (w2) ->
  * head mix (W2) -> @V, for batch elements [0,B) and query rows [q_row_begin, q_row_end).
  * Replaces the body of MTAAttentionTriton.forward (mta_attention_triton.py:61-92) with use_mask=False;

@@ -34,6 +34,8 @@ SIGNATURES = {
     "mta_pv_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mta_conv_attn_workspace_bytes": (_sz, [_i] * 7),
     "mta_conv_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
+    "mta_static_scratch_bytes": (_sz, []),
+    "mta_conv_attn_fwd_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_workspace_bytes": (_sz, [_i] * 11),
     "mta_fused_fwd": (_i, [_vp] * 9 + [_sz] + [_i] * 13 + [_vp]),
 }
