@@ -12,6 +12,7 @@ thread_local long g_launches = 0;
 int g_variant_head_linear = 0;
 int g_variant_conv2d = 0;
 int g_variant_gemm = 0;
+int g_variant_fused = 0;
 }  // namespace
 
 void set_error(const char* fmt, ...) {
@@ -27,6 +28,7 @@ int variant(const char* key) {
     if (!strcmp(key, "head_linear")) return g_variant_head_linear;
     if (!strcmp(key, "conv2d")) return g_variant_conv2d;
     if (!strcmp(key, "gemm")) return g_variant_gemm;
+    if (!strcmp(key, "fused")) return g_variant_fused;
     return 0;
 }
 
@@ -62,6 +64,7 @@ int mta_set_variant(const char* key, int value) {
     if (!strcmp(key, "head_linear")) g_variant_head_linear = value;
     else if (!strcmp(key, "conv2d")) g_variant_conv2d = value;
     else if (!strcmp(key, "gemm")) g_variant_gemm = value;
+    else if (!strcmp(key, "fused")) g_variant_fused = value;
     else return MTA_ERR_INVALID;
     return MTA_OK;
 }

@@ -48,15 +48,21 @@ using namespace tc05;
 #ifdef MTA_CONV_PROFILE
 __device__ long long g_prof[32];
 #define PROF_START long long prof_t = clock64();
-#define PROF_ACC(slot, cond)                                                   \
-    {                                                                          \
-        const long long prof_n = clock64();                                    \
-        if (blockIdx.x == 0 && lane == 0 && (cond)) g_prof[slot] += prof_n - prof_t; \
-        prof_t = prof_n;                                                       \
+#define PROF_DECL long long prof_loc[4] = {0, 0, 0, 0};
+#define PROF_ACC(slot, cond)                        \
+    {                                               \
+        const long long prof_n = clock64();         \
+        prof_loc[(slot) & 3] += prof_n - prof_t;    \
+        prof_t = prof_n;                            \
     }
+#define PROF_FLUSH(base, cond)                                                          \
+    if (blockIdx.x == 0 && lane == 0 && (cond))                                         \
+        for (int pi = 0; pi < 4; ++pi) g_prof[(base) + pi] = prof_loc[pi];
 #else
 #define PROF_START
+#define PROF_DECL
 #define PROF_ACC(slot, cond)
+#define PROF_FLUSH(base, cond)
 #endif
 
 constexpr int TM = 128;            // output rows per tile = MMA M
@@ -194,6 +200,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
+            PROF_DECL
             TileIter it;
             it.init(g, t_begin);
             for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
@@ -204,12 +211,14 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 mbar_expect_tx(&raw_full[st], (uint32_t)(TH * RAWC * 2));
                 tma_load_3d(raw_base + st * raw_bytes, &mx, &raw_full[st], it.n0() - pad8, it.m0(g) - (R - 1) - g.x_row0, it.plane);
             }
+            PROF_FLUSH(12, true)
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         constexpr uint32_t idesc32 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 32);
         constexpr uint32_t idesc16 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 16);
         const uint32_t lbo_a = (uint32_t)(NMAT * 128);
+        PROF_DECL
         for (int n = 0; n < my_tiles; ++n) {
             const int pk = n % NPK, ab = n & 1;
             PROF_START
@@ -254,6 +263,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             __syncwarp();
             PROF_ACC(3, true)
         }
+        PROF_FLUSH(0, true)
     } else if (warp < 6) {
         // ---------------- repack (+ causal zeroing) and Toeplitz slices ----------------
         const int ft = tid - 64;          // 0..127
@@ -263,6 +273,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         TileIter it;
         it.init(g, t_begin);
         int prev_head[NPK];
+        PROF_DECL
 #pragma unroll
         for (int i = 0; i < NPK; ++i) prev_head[i] = -1;
         for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
@@ -340,6 +351,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             }
             PROF_ACC(7, warp == 2)
         }
+        PROF_FLUSH(4, warp == 2)
     } else {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;
@@ -347,6 +359,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         const int mrow = quarter * 32 + lane;                // accumulator row (TMEM lane) this thread owns ...
         const int row = (mrow >> 3) + 16 * (mrow & 7);       // ... which is this row of the tile
         uint8_t* orow = out_base + row * 128;
+        PROF_DECL
         TileIter it;
         it.init(g, t_begin);
         for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
@@ -401,6 +414,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             }
             PROF_ACC(11, warp == 6)
         }
+        PROF_FLUSH(8, warp == 6)
         if (issuer) bulk_wait_all();
     }
     fence_before_sync();
@@ -475,7 +489,7 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
         const long n0 = (g.total_tiles + grid - 1) / grid;
         fprintf(stderr, "conv2d_tc05 clk/tile (CTA 0, %ld tiles): producer wait_empty %lld | mma wait_ready %lld wait_acc %lld issue %lld | "
                 "repack wait_free %lld toeplitz %lld wait_raw %lld move %lld | epilogue wait_acc %lld wait_store %lld drain %lld store %lld\n",
-                n0, h[0] / n0, h[1] / n0, h[2] / n0, h[3] / n0, h[4] / n0, h[5] / n0, h[6] / n0, h[7] / n0, h[8] / n0, h[9] / n0,
+                n0, h[12] / n0, h[1] / n0, h[2] / n0, h[3] / n0, h[4] / n0, h[5] / n0, h[6] / n0, h[7] / n0, h[8] / n0, h[9] / n0,
                 h[10] / n0, h[11] / n0);
     }
 #endif

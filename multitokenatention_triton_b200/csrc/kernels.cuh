@@ -42,6 +42,14 @@ int qk_scores_simt_launch(const void* q, const void* k, void* s, PlaneView sv, i
 int pv_simt_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
                    int row_begin, int row_end, int dtype, cudaStream_t st);
 
+// Fused conv + head mix stage (conv_mix.cu): 16-bit dtypes, causal, C <= 16 heads, S <= 17, W a multiple of 8.
+bool conv_mix_supported(int C, int W, int R, int S, int causal, int dtype, int w_dtype, const void* x, const void* y);
+size_t conv_mix_table_bytes(int C, int R, int w_dtype);
+int conv_mix_prepare(const void* w, int w_dtype, int C, int R, int S, int dtype, void* table, cudaStream_t st);
+int conv_mix_launch(const void* x, PlaneView xv, long x_rows_stored, const void* table, const void* Wm, int w_dtype, void* y,
+                    PlaneView yv, int N, int C, int W, int R, int S, int row_begin, int row_end, const void* stats_in,
+                    void* stats_out, int stats_row0, int stats_rows, int dtype, cudaStream_t st);
+
 // tcgen05 version of the conv (conv2d_tc05.cu): 16-bit dtypes, S <= 17, W a multiple of 8, R small enough for its
 // shared-memory rings (R <= 13 with 16-bit weights).
 bool conv2d_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int W, int R, int S, int dtype,

@@ -242,6 +242,29 @@ def test_mta_forward(name, fused, golden):
         assert_parity(got, staged, wl.dtype, f"{name} vs stage-rounded oracle")
 
 
+@pytest.mark.parametrize("name", ["s130_6x11_bf16", "s128_11x15_bf16"])
+def test_mta_forward_fused_stages_agree_with_stage_by_stage(name):
+    """The two fused conv + head-mix launches keep the rounding points of the seven-launch pipeline, so the two agree
+    to a few ulps of the 16-bit dtype (summation order and the exp differ)."""
+    wl = MTA_CASES[name]
+    inp = make_mta_inputs(wl)
+    d = {k: t.to(DEV) for k, t in inp.items()}
+    args = [d[n] for n in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    staged = ops.mta_fused_fwd(*args, True)
+    _lib.set_variant("fused", 2)
+    try:
+        fused = ops.mta_fused_fwd(*args, True)
+        part = torch.zeros_like(fused)
+        ops.mta_fused_fwd(*args, True, rows=(33, 97), out=part)
+    finally:
+        _lib.set_variant("fused", 0)
+    _lib.device_status()
+    assert rel_fro(npf(fused), npf(staged)) <= 4e-3 and rel_max(npf(fused), npf(staged)) <= 2e-2
+    assert torch.equal(part[:, :, 33:97], fused[:, :, 33:97])
+    a = [npf(inp[k]) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    assert_parity(npf(fused), orc.mta_fwd(*a, True, orc.ROUND_NONE), wl.dtype, f"{name} fused stages vs oracle")
+
+
 @pytest.mark.parametrize("name,rows", [("ragged_f32", (3, 20)), ("ragged_f32", (64, 65)), ("s130_6x11_bf16", (17, 130)),
                                        ("c1", (100, 164)), ("s192_h32_f16", (0, 9))])
 def test_mta_forward_row_range(name, rows):
