@@ -64,6 +64,12 @@ int qk_scores_tc05_launch(const void* q, const void* k, void* s, PlaneView sv, i
                           int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 int pv_tc05_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
                    int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
+// Persistent, warp-specialised score-tile kernel (qk_persistent.cu); same domain as the kernels above.
+// NI = 1: c = scale * a b^T.  mode 0: all tiles with keys <= query; 1 / 2: the band of a (band_cq x (2 band_pw + 1))
+// conv / the tiles wholly below it.
+int qk_persistent_launch(const void* a, const void* b, void* c, PlaneView cv, int B, int H, int S, int D, int NI, float scale,
+                         int round_scale, int causal, int mode, int band_cq, int band_pw, int row_begin, int row_end, int dtype,
+                         cudaStream_t st);
 // Reads and clears the flag raised by a device-side bounded wait that gave up (synchronises `st`).
 int device_wait_status(cudaStream_t st, int* timed_out);
 

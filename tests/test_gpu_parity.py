@@ -166,12 +166,13 @@ def test_softmax(S, dtype):
     one_stage_close(npf(y2), ref, dtype, f"softmax of -inf filled S={S}")
 
 
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("S,D", [(5, 8), (65, 16), (130, 64), (256, 128), (128, 64), (200, 128), (8, 64), (1000, 128)])
 def test_contractions(S, D, dtype, variant):
-    """variant 1 = CUDA-core kernels, 2 = tcgen05 tensor-core kernels (16-bit dtypes, D in {64,128}, S % 8 == 0)."""
-    if variant == 2 and (dtype == torch.float32 or D not in (64, 128) or S % 8):
+    """variant 1 = CUDA-core kernels, 2 = tcgen05 kernels (16-bit dtypes, D in {64,128}, S % 8 == 0; persistent score
+    kernel), 3 = the same with the one-CTA-per-tile score kernel."""
+    if variant >= 2 and (dtype == torch.float32 or D not in (64, 128) or S % 8):
         pytest.skip("outside the tensor-core kernels' domain")
     _lib.set_variant("gemm", variant)
     try:
