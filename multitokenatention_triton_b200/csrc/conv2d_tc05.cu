@@ -8,28 +8,25 @@
 //
 // Persistent, warp-specialised kernel: one CTA per SM walks a contiguous range of 128 x 128 output tiles
 // (only tiles that touch keys <= query when causal):
-//   warp 0      TMA producer: one tiled load per tile of the (128 + R-1) x 152 halo tile, row-major, into a
-//               2-stage ring (out-of-range rows / columns arrive as zero = the conv's zero padding)
-//   warps 2-5   repack the tile into the layout the MMA reads, zeroing keys above the causal diagonal on the
-//               way (2-stage ring); rebuild the Toeplitz slices when the head changes
-//   warp 1      issues the MMAs (54 per tile for a 6 x 11 kernel) into TMEM accumulator n % 2
-//   warps 6-9   epilogue: TMEM -> registers -> 16-bit -> swizzled shared-memory tile -> TMA tiled store (a thread
+//   warp 0      TMA producer: three 64-column boxes per tile bring the (128 + R-1) x 192 halo tile straight into the
+//               128-byte-swizzled K-major layout the MMA reads (3-stage ring; out-of-range rows / columns arrive as
+//               zero = the conv's zero padding)
+//   warps 2-3   zero the keys above the causal diagonal in the staged tile (diagonal tiles only); rebuild the
+//               Toeplitz slices when the head changes
+//   warps 1,8,9 issue the MMAs (54 per tile for a 6 x 11 kernel, split by row tap) into TMEM accumulator n % 2
+//   warps 4-7   epilogue: TMEM -> registers -> 16-bit -> swizzled shared-memory tile -> TMA tiled store (a thread
 //               owns one output row, so direct global stores would touch 32 different lines per instruction)
 //
 // MMA schedule.  Staged column sc holds key n0 - 8 + sc; output column x reads staged columns x + a_off + j
 // (a_off = 8 - pad_w).  A k-step is 16 staged columns [16 s, 16 s + 16), s = 0..8; it contributes to the two
-// 16-column output blocks s-1 and s, so there is one MMA (M = 128 rows, N = 32, K = 16) per (row tap i, k-step s),
-// against the 32 x 16 Toeplitz slice of row tap i, element (n', kk) = w[i][kk + 16 - n' - a_off] (the same for
-// every s).  The first and last k-step touch one block only (N = 16, half of the slice).  For i = 0 the even
-// k-steps go first with accumulate = 0 (they touch every block exactly once), then the odd ones.
-// Measured: at M = 128 a tcgen05.mma costs ~44 cycles for any N <= 64 (operand fetch), and about twice that
-// when its 8-row x 16-byte core matrices straddle 128-byte lines, so the schedule minimises the MMA count and
-// the layout keeps every core matrix aligned:
-//
-// Layout of the repacked tile (no swizzle, K-major).  MMA row m = 8 g + t stands for tile row g + 16 t, so core
-// matrix g of a k chunk holds staged rows {g + 16 t : t = 0..7} - and the rows a row tap i needs, g + i + 16 t,
-// are simply core matrix g + i.  A k chunk (8 staged columns) is 16 + R-1 core matrices of 128 bytes (rows whose
-// index mod 16 is below R-1 are stored twice); a row tap is a 128-byte offset of the descriptor's start address.
+// 16-column output blocks s-1 and s, so there is one MMA (M = 128 rows, N = 32, K = 16) per (row tap i, k-step s):
+//   A = staged rows i .. i+127, columns 16 s .. 16 s + 15.  In the swizzled layout a row is 128 bytes and the swizzle
+//       is a function of the shared-memory address alone, so a row tap is just the descriptor's start address
+//       advanced by i * 128 bytes (measured: correct for every i with the base-offset field left at 0);
+//   B = the 32 x 16 Toeplitz slice of row tap i, element (n', kk) = w[i][kk + 16 - n' - a_off] - the same for every s.
+// The first and last k-step touch one block only (N = 16, half of the slice).  For i = 0 the even k-steps go first
+// with accumulate = 0 (they touch every block exactly once), then the odd ones.  Measured: at M = 128 a
+// tcgen05.mma costs ~44 cycles for any N <= 64, which is why the schedule minimises the MMA count, not the MACs.
 #include <cstdlib>
 
 #include "kernels.cuh"
@@ -70,10 +67,10 @@ constexpr int TN = 128;            // output columns per tile
 constexpr int NB = TN / 16;        // 16-column blocks
 constexpr int NKS = 9;             // k-steps of 16 staged columns: 8 (left halo) + 128 + 8
 constexpr int NCH = 2 * NKS;       // staged 8-column chunks
-constexpr int RAWC = 152;          // columns of the row-major staging tile (pitch 304 B = 19 x 16: conflict-free repack)
-constexpr int NRAW = 2;            // stages of the row-major ring
-constexpr int NPK = 2;             // stages of the repacked ring
+constexpr int NBOX = 3;            // 64-column TMA boxes per staged tile
+constexpr int NSTAGE = 3;
 constexpr int OUT_BYTES = 2 * TM * 128;   // output staging: two 64-column boxes of 128 rows x 128 bytes, 128-byte swizzle
+constexpr int NISS = 3;            // MMA-issuing threads (warps 1, 8, 9)
 constexpr int THREADS = 320;
 
 template <typename T> struct AbFmt;
@@ -143,19 +140,17 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                    const void* __restrict__ w, int w_dtype, int y_row0, ConvGeom g, int* err_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t raw_full[NRAW], raw_empty[NRAW], pk_ready[NPK], pk_empty[NPK], acc_full[2], acc_empty[2];
+    __shared__ __align__(8) uint64_t full_bar[NSTAGE], ready_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2], init_bar[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ uint4 sched[2 * 16 * NKS];      // MMA schedule of one tile (R <= 16 row taps, two terms for fp32 weights)
     const int R = g.R, S = g.S;
     const int TH = TM + R - 1;
-    const int NMAT = 16 + R - 1;                               // core matrices per k chunk
-    const int raw_bytes = (TH * RAWC * 2 + 127) & ~127;
-    const int xa_bytes = NCH * NMAT * 128;
-    const int tb_bytes = R * 1024 * (g.split_w ? 2 : 1);      // Toeplitz slices: 32 x 16 per row tap
-    const int pk_bytes = xa_bytes + tb_bytes;
+    const int box_bytes = (TH * 128 + 1023) & ~1023;          // one 64-column box, 1024-byte aligned (swizzle period)
+    const int tb_bytes = (R * 1024 * (g.split_w ? 2 : 1) + 1023) & ~1023;   // Toeplitz slices: 32 x 16 per row tap
+    const int stage_bytes = NBOX * box_bytes + tb_bytes;
     uint8_t* out_base = smem;                                  // 1024-byte aligned, as the swizzled TMA store needs
-    uint8_t* raw_base = smem + OUT_BYTES;
-    uint8_t* pk_base = raw_base + NRAW * raw_bytes;
+    uint8_t* stage_base = smem + OUT_BYTES;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pad_w = (S - 1) / 2;
     const int pad8 = (pad_w + 7) & ~7;
@@ -173,16 +168,14 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < NRAW; ++i) {
-                mbar_init(&raw_full[i], 1);
-                mbar_init(&raw_empty[i], 4);
-            }
-            for (int i = 0; i < NPK; ++i) {
-                mbar_init(&pk_ready[i], 4);
-                mbar_init(&pk_empty[i], 1);
+            for (int i = 0; i < NSTAGE; ++i) {
+                mbar_init(&full_bar[i], 1);
+                mbar_init(&ready_bar[i], 2);
+                mbar_init(&empty_bar[i], NISS);
             }
             for (int i = 0; i < 2; ++i) {
-                mbar_init(&acc_full[i], 1);
+                mbar_init(&acc_full[i], NISS);
+                mbar_init(&init_bar[i], 1);
                 mbar_init(&acc_empty[i], 4);
             }
             fence_mbar_init();
@@ -191,6 +184,25 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         }
         __syncwarp();
         tmem_alloc(&tmem_slot, 2 * TN);
+    } else if (warp == 1 && lane == 0) {
+        // MMA schedule of one tile, in issue order: batch (row tap i, term) x nine k-steps, even k-steps first (for
+        // i = 0 they carry accumulate = 0 and touch every 16-column block exactly once).  Per MMA: A offset and B offset
+        // in 16-byte units from the stage base, accumulator column, flags (bit 0: N = 16, bit 1: accumulate).
+        int m = 0;
+        for (int i = 0; i < R; ++i)
+            for (int part = 0; part < (g.split_w ? 2 : 1); ++part)
+                for (int pass = 0; pass < 2; ++pass)
+                    for (int s = pass; s < NKS; s += 2) {
+                        const uint32_t a16 = (uint32_t)(((s / 4) * box_bytes + i * 128 + (s % 4) * 32) >> 4);
+                        // Toeplitz slice of row tap i: 32 rows (n') x 16 (kk); the first k-step only touches block 0
+                        // (rows 16..31 of the slice, +256 bytes), the last one only block 7 (rows 0..15)
+                        uint32_t b16 = (uint32_t)((NBOX * box_bytes + i * 1024 + part * R * 1024) >> 4);
+                        if (s == 0) b16 += 16;
+                        const uint32_t dcol = s == 0 ? 0u : 16u * (uint32_t)(s - 1);
+                        const uint32_t n16 = (s == 0 || s == NKS - 1) ? 1u : 0u;
+                        const uint32_t acc = (i > 0 || pass > 0 || part > 0) ? 1u : 0u;
+                        sched[m++] = make_uint4(a16, b16, dcol, n16 | (acc << 1));
+                    }
     }
     fence_before_sync();
     __syncthreads();
@@ -204,94 +216,89 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             TileIter it;
             it.init(g, t_begin);
             for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
-                const int st = n % NRAW;
+                const int st = n % NSTAGE;
                 PROF_START
-                mbar_wait(&raw_empty[st], ((n / NRAW) & 1) ^ 1, err_flag);
+                mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
                 PROF_ACC(0, true)
-                mbar_expect_tx(&raw_full[st], (uint32_t)(TH * RAWC * 2));
-                tma_load_3d(raw_base + st * raw_bytes, &mx, &raw_full[st], it.n0() - pad8, it.m0(g) - (R - 1) - g.x_row0, it.plane);
+                uint8_t* xa = stage_base + st * stage_bytes;
+                mbar_expect_tx(&full_bar[st], (uint32_t)(NBOX * TH * 128));
+#pragma unroll
+                for (int j = 0; j < NBOX; ++j)
+                    tma_load_3d(xa + j * box_bytes, &mx, &full_bar[st], it.n0() - pad8 + 64 * j, it.m0(g) - (R - 1) - g.x_row0,
+                                it.plane);
             }
             PROF_FLUSH(12, true)
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp == 1 || warp >= 8) {
+        // ---------------- MMA issuers ----------------
+        // Issuing a tcgen05.mma whose descriptors differ from the previous one costs the issuing thread ~100 cycles
+        // here (measured), about twice the ~47 cycles the tensor core needs for it, so three threads issue: issuer k
+        // takes the row taps (and, for fp32 weights, remainder terms) k, k+3, ...  Only the accumulate = 0 MMAs must
+        // come first; they are in batch 0, and issuer 0 releases the others through init_bar once they are issued.
         constexpr uint32_t idesc32 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 32);
         constexpr uint32_t idesc16 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 16);
-        const uint32_t lbo_a = (uint32_t)(NMAT * 128);
+        const int n_batch = R * (g.split_w ? 2 : 1);
+        const int issuer = warp == 1 ? 0 : warp - 7;          // 0, 1, 2
         PROF_DECL
         for (int n = 0; n < my_tiles; ++n) {
-            const int pk = n % NPK, ab = n & 1;
+            const int st = n % NSTAGE, ab = n & 1;
             PROF_START
-            mbar_wait(&pk_ready[pk], (n / NPK) & 1, err_flag);
+            mbar_wait(&ready_bar[st], (n / NSTAGE) & 1, err_flag);
             PROF_ACC(1, true)
             mbar_wait(&acc_empty[ab], ((n >> 1) & 1) ^ 1, err_flag);
+            if (issuer != 0) mbar_wait(&init_bar[ab], (n >> 1) & 1, err_flag);
             PROF_ACC(2, true)
             fence_after_sync();
             if (lane == 0) {
-                const uint32_t xa_addr = smem_u32(pk_base + pk * pk_bytes), tb_addr = xa_addr + (uint32_t)xa_bytes;
+                const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
+                const uint64_t da0 = smem_desc_sw128(xa_addr, 16, 1024);
+                const uint64_t db0 = smem_desc_plain(xa_addr, 512, 128);     // k chunks 512 bytes apart, 8-row groups 128
                 const uint32_t d0 = tmem + (uint32_t)(ab * TN);
-                const uint64_t da0 = smem_desc_plain(xa_addr, lbo_a, 128);
-                for (int i = 0; i < R; ++i) {
-                    // Toeplitz slice of row tap i: 32 rows (n') x 16 (kk); k chunks 512 bytes apart, 8-row groups 128 bytes apart
-                    const uint64_t db32 = smem_desc_plain(tb_addr + (uint32_t)(i * 1024), 512, 128);
-                    const uint64_t db_up = db32 + 16;            // rows 16..31: +256 bytes
-                    const uint64_t dl32 = db32 + (uint64_t)(R * 64);
-                    const uint64_t dl_up = dl32 + 16;
-                    const uint64_t da_i = da0 + (uint64_t)(i * 8);   // row tap: +128 bytes
+                // the nine table entries of a batch are fetched before its MMAs are issued
+                for (int b = issuer; b < n_batch; b += NISS) {
+                    uint4 e[NKS];
 #pragma unroll
-                    for (int pass = 0; pass < 2; ++pass) {
+                    for (int j = 0; j < NKS; ++j) e[j] = sched[b * NKS + j];
 #pragma unroll
-                        for (int s = pass; s < NKS; s += 2) {      // even k-steps first: for i = 0 they initialise every block
-                            const uint64_t da = da_i + (uint64_t)(2 * s) * (uint64_t)(NMAT * 8);
-                            const uint32_t acc = (i > 0 || pass > 0) ? 1u : 0u;
-                            if (s == 0) {                           // touches block 0 only: upper half of the slice
-                                mma_f16_ss(d0, da, db_up, idesc16, acc);
-                                if (g.split_w) mma_f16_ss(d0, da, dl_up, idesc16, 1u);
-                            } else if (s == NKS - 1) {              // touches block 7 only: lower half of the slice
-                                mma_f16_ss(d0 + 16u * (NB - 1), da, db32, idesc16, acc);
-                                if (g.split_w) mma_f16_ss(d0 + 16u * (NB - 1), da, dl32, idesc16, 1u);
-                            } else {
-                                mma_f16_ss(d0 + 16u * (s - 1), da, db32, idesc32, acc);
-                                if (g.split_w) mma_f16_ss(d0 + 16u * (s - 1), da, dl32, idesc32, 1u);
-                            }
-                        }
-                    }
+                    for (int j = 0; j < NKS; ++j)
+                        mma_f16_ss(d0 + e[j].z, da0 + e[j].x, db0 + e[j].y, (e[j].w & 1u) ? idesc16 : idesc32, e[j].w >> 1);
+                    if (b == 0) mbar_arrive(&init_bar[ab]);
                 }
-                mma_commit(&pk_empty[pk]);
+                mma_commit(&empty_bar[st]);
                 mma_commit(&acc_full[ab]);
             }
             __syncwarp();
             PROF_ACC(3, true)
         }
-        PROF_FLUSH(0, true)
-    } else if (warp < 6) {
-        // ---------------- repack (+ causal zeroing) and Toeplitz slices ----------------
-        const int ft = tid - 64;          // 0..127
-        // Thread ft moves staged row sr = c + 16 t with t = ft % 8, c = (ft / 8 + ft % 8) % 16: eight consecutive lanes
-        // read rows 17 (or 1) apart and write the eight rows of different core matrices - no bank conflicts either way.
-        const int rt = ft & 7, rc = ((ft >> 3) + rt) & 15;
+        PROF_FLUSH(0, warp == 1)
+    } else if (warp < 4) {
+        // ---------------- (warps 2-3) causal zeroing of the staged tile, Toeplitz slices ----------------
+        const int ft = tid - 64;          // 0..63
         TileIter it;
         it.init(g, t_begin);
-        int prev_head[NPK];
+        int prev_head[NSTAGE];
         PROF_DECL
 #pragma unroll
-        for (int i = 0; i < NPK; ++i) prev_head[i] = -1;
+        for (int i = 0; i < NSTAGE; ++i) prev_head[i] = -1;
         for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
-            const int st = n % NRAW, pk = n % NPK;
+            const int st = n % NSTAGE;
             const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
             const int head = plane % g.C;
-            const uint8_t* raw = raw_base + st * raw_bytes;
-            uint8_t* xa = pk_base + pk * pk_bytes;
-            uint8_t* tb = xa + xa_bytes;
-            // the repacked stage (and its Toeplitz slices) is free once the MMAs of tile n - NPK are done
+            uint8_t* xa = stage_base + st * stage_bytes;
+            uint8_t* tb = xa + NBOX * box_bytes;
+            // the stage (and its Toeplitz slices) is free once the MMAs of tile n - NSTAGE are done
             PROF_START
-            mbar_wait(&pk_empty[pk], ((n / NPK) & 1) ^ 1, err_flag);
+            mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
             PROF_ACC(4, warp == 2)
-            const int ph = (pk == 0) ? prev_head[0] : prev_head[1];
-            if (pk == 0) prev_head[0] = head; else prev_head[1] = head;
+            int ph = -1;
+#pragma unroll
+            for (int i = 0; i < NSTAGE; ++i)
+                if (i == st) { ph = prev_head[i]; prev_head[i] = head; }
             if (ph != head) {
+                // slice of row tap i, element (n', kk) = w[i][kk + 16 - n' - a_off]; no-swizzle K-major layout:
+                // 8 rows x 16 bytes per core matrix, the two k chunks 512 bytes apart, row groups 128 bytes apart
                 const int total = R * 512;
-                for (int idx = ft; idx < total; idx += 128) {
+                for (int idx = ft; idx < total; idx += 64) {
                     const int i = idx / 512, e = idx % 512;
                     const int nn = e / 16, kk = e % 16;
                     const int j = kk + 16 - nn - a_off;
@@ -303,61 +310,40 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 }
             }
             PROF_ACC(5, warp == 2)
-            mbar_wait(&raw_full[st], (n / NRAW) & 1, err_flag);
+            mbar_wait(&full_bar[st], (n / NSTAGE) & 1, err_flag);
             PROF_ACC(6, warp == 2)
-            // staged row sr is query m0-(R-1)+sr; chunk ch holds keys n0-pad8+8ch .. +7
-            const bool diag = g.causal && n0 - pad8 + NCH * 8 - 1 > m0 - (R - 1);
-#pragma unroll 1
-            for (int pass = 0; pass < 2; ++pass) {
-                // pass 0: rows 0..127 at (matrix sr%16, slot sr/16) and, when sr >= 16 and sr%16 < R-1, again at
-                // (matrix 16 + sr%16, slot sr/16 - 1); pass 1: rows 128..TH-1, which only have the second position
-                int sr, off0, off1;
-                if (pass == 0) {
-                    sr = rc + 16 * rt;
-                    off0 = (rc * 8 + rt) * 16;
-                    off1 = (rt >= 1 && rc < R - 1) ? ((16 + rc) * 8 + rt - 1) * 16 : -1;
-                } else {
-                    if (ft >= R - 1) break;
-                    sr = 128 + ft;
-                    off0 = ((16 + ft) * 8 + 7) * 16;
-                    off1 = -1;
-                }
-                const uint8_t* src = raw + sr * (RAWC * 2);
-                const int qq = m0 - (R - 1) + sr;
-#pragma unroll 6
-                for (int ch = 0; ch < NCH; ++ch) {
-                    uint4 v = *reinterpret_cast<const uint4*>(src + ch * 16);
-                    if (diag) {
-                        const int kfirst = n0 - pad8 + ch * 8;
-                        if (kfirst > qq) {
-                            v = make_uint4(0u, 0u, 0u, 0u);
-                        } else if (kfirst + 7 > qq) {
-                            uint16_t* e16 = reinterpret_cast<uint16_t*>(&v);
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (kfirst + e > qq) e16[e] = 0;
-                        }
+            // staged row sr is query m0-(R-1)+sr; staged column sc is key n0-pad8+sc, in box sc/64 at byte
+            // sr*128 + (((sc%64)/8) ^ (sr%8))*16 + (sc%8)*2.  Zero the keys above the query.
+            if (g.causal && n0 - pad8 + NCH * 8 - 1 > m0 - (R - 1)) {
+                // one thread per staged row: zero from the first key above the query to the end of the row
+                const int c0 = n0 - pad8;
+                for (int sr = ft; sr < TH; sr += 64) {
+                    const int qq = m0 - (R - 1) + sr;
+                    int first = qq - c0 + 1;                      // first staged column to zero
+                    if (first >= NCH * 8) continue;
+                    if (first < 0) first = 0;
+                    int ch = first >> 3;
+                    uint8_t* rowp = xa + sr * 128;
+                    if (first & 7) {
+                        uint16_t* e16 = reinterpret_cast<uint16_t*>(rowp + (ch >> 3) * box_bytes + (((ch & 7) ^ (sr & 7)) << 4));
+                        for (int e = first & 7; e < 8; ++e) e16[e] = 0;
+                        ++ch;
                     }
-                    uint8_t* dch = xa + ch * NMAT * 128;
-                    *reinterpret_cast<uint4*>(dch + off0) = v;
-                    if (off1 >= 0) *reinterpret_cast<uint4*>(dch + off1) = v;
+                    for (; ch < NCH; ++ch)
+                        *reinterpret_cast<uint4*>(rowp + (ch >> 3) * box_bytes + (((ch & 7) ^ (sr & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
             fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&raw_empty[st]);
-                mbar_arrive(&pk_ready[pk]);
-            }
+            if (lane == 0) mbar_arrive(&ready_bar[st]);
             PROF_ACC(7, warp == 2)
         }
         PROF_FLUSH(4, warp == 2)
     } else {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;
-        const bool issuer = (warp == 6 && lane == 0);
-        const int mrow = quarter * 32 + lane;                // accumulator row (TMEM lane) this thread owns ...
-        const int row = (mrow >> 3) + 16 * (mrow & 7);       // ... which is this row of the tile
+        const bool issuer = (warp == 4 && lane == 0);
+        const int row = quarter * 32 + lane;                 // row of the tile this thread owns
         uint8_t* orow = out_base + row * 128;
         PROF_DECL
         TileIter it;
@@ -369,10 +355,10 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             mbar_wait(&acc_full[ab], (n >> 1) & 1, err_flag);
             __syncwarp();
             fence_after_sync();
-            PROF_ACC(8, warp == 6)
+            PROF_ACC(8, warp == 4)
             if (issuer) bulk_wait_read();                    // the previous tile's store has finished reading the staging tile
             named_barrier(1, 128);
-            PROF_ACC(9, warp == 6)
+            PROF_ACC(9, warp == 4)
             const int q = m0 + row;
 #pragma unroll 1
             for (int cblk = 0; cblk < TN / 32; ++cblk) {
@@ -403,7 +389,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[ab]);
-            PROF_ACC(10, warp == 6)
+            PROF_ACC(10, warp == 4)
             fence_proxy_async();                             // staging tile written through the generic proxy, read by TMA
             named_barrier(1, 128);
             if (issuer) {
@@ -412,9 +398,9 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 if (n0 + 64 < g.W) tma_store_3d(&my, out_base + TM * 128, n0 + 64, m0 - y_row0, plane);
                 bulk_commit();
             }
-            PROF_ACC(11, warp == 6)
+            PROF_ACC(11, warp == 4)
         }
-        PROF_FLUSH(8, warp == 6)
+        PROF_FLUSH(8, warp == 4)
         if (issuer) bulk_wait_all();
     }
     fence_before_sync();
@@ -438,8 +424,9 @@ fill_above_kernel(T* __restrict__ y, PlaneView yv, int W, int row_begin, int row
 
 size_t conv2d_tc05_smem_bytes(int R, bool split_w) {
     const int TH = TM + R - 1;
-    return (size_t)1024 + OUT_BYTES + (size_t)NRAW * ((TH * RAWC * 2 + 127) & ~127) +
-           (size_t)NPK * ((size_t)NCH * (16 + R - 1) * 128 + (size_t)R * 1024 * (split_w ? 2 : 1));
+    const size_t box = (size_t)((TH * 128 + 1023) & ~1023);
+    const size_t tb = (size_t)((R * 1024 * (split_w ? 2 : 1) + 1023) & ~1023);
+    return 1024 + OUT_BYTES + NSTAGE * (NBOX * box + tb);
 }
 
 template <typename T>
@@ -450,7 +437,7 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
     int rc;
     const int TH = TM + R - 1;
     if ((rc = make_tensor_map_3d(&mx, x, (uint64_t)planes, (uint64_t)x_rows_stored, (uint64_t)W, (uint64_t)xv.width,
-                                 (uint64_t)xv.plane_stride, RAWC, (uint32_t)TH, false)))
+                                 (uint64_t)xv.plane_stride, 64, (uint32_t)TH, true)))
         return rc;
     int* flag = nullptr;
     if ((rc = wait_flag_ptr(&flag))) return rc;
@@ -488,7 +475,7 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
         cudaMemcpyToSymbol(g_prof, z, sizeof(z));
         const long n0 = (g.total_tiles + grid - 1) / grid;
         fprintf(stderr, "conv2d_tc05 clk/tile (CTA 0, %ld tiles): producer wait_empty %lld | mma wait_ready %lld wait_acc %lld issue %lld | "
-                "repack wait_free %lld toeplitz %lld wait_raw %lld move %lld | epilogue wait_acc %lld wait_store %lld drain %lld store %lld\n",
+                "fixup wait_free %lld toeplitz %lld wait_full %lld zeroing %lld | epilogue wait_acc %lld wait_store %lld drain %lld store %lld\n",
                 n0, h[12] / n0, h[1] / n0, h[2] / n0, h[3] / n0, h[4] / n0, h[5] / n0, h[6] / n0, h[7] / n0, h[8] / n0, h[9] / n0,
                 h[10] / n0, h[11] / n0);
     }
@@ -506,7 +493,7 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
 
 bool conv2d_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int W, int R, int S, int dtype,
                            int w_dtype) {
-    return dtype != MTA_F32 && S <= 17 && conv2d_tc05_smem_bytes(R, w_dtype == MTA_F32) <= 227 * 1024 && W % 8 == 0 && xv.width == W && yv.width == W &&
+    return dtype != MTA_F32 && S <= 17 && R <= 16 && conv2d_tc05_smem_bytes(R, w_dtype == MTA_F32) <= 227 * 1024 && W % 8 == 0 && xv.width == W && yv.width == W &&
            xv.plane_stride % 8 == 0 && yv.plane_stride % 8 == 0 && aligned16(x) && aligned16(y);
 }
 

@@ -57,6 +57,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        // Back off: hundreds of threads polling barriers in shared memory slow down the tensor core's operand reads.
+        if (i >= 4) __nanosleep(i < 64 ? 64 : 256);
         // once any wait on the device has given up, every other one gives up quickly
         if ((i & 1023u) == 1023u && *reinterpret_cast<volatile int*>(err_flag) != 0) return false;
     }
@@ -134,14 +136,15 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(int ab_format, int a_mn_ma
            ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
+// D[tmem] (+)= A[smem] * B[smem]; issued by one thread.  No "memory" clobber: the instruction is ordered against the
+// barriers and fences around it because all of them are volatile asm statements, and a clobber would stop the
+// compiler from overlapping the issuing thread's own loads with the MMAs it issues.
 __device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate));
 }
 // Arrive on `bar` once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
