@@ -8,14 +8,15 @@
 //
 // Persistent, warp-specialised kernel: one CTA per SM walks a contiguous range of 128 x 128 output tiles
 // (only tiles that touch keys <= query when causal):
-//   warp 0      TMA producer: three 64-column boxes per tile bring the (128 + R-1) x 192 halo tile straight into the
-//               128-byte-swizzled K-major layout the MMA reads (3-stage ring; out-of-range rows / columns arrive as
+//   warp 0      TMA producer: two 64-column boxes (128-byte swizzle) and one 16-column box (32-byte swizzle) per tile
+//               bring the (128 + R-1) x 144 halo tile straight into the swizzled K-major layouts the MMA reads (3-stage ring; out-of-range rows / columns arrive as
 //               zero = the conv's zero padding)
 //   warps 2-3   zero the keys above the causal diagonal in the staged tile (diagonal tiles only); rebuild the
 //               Toeplitz slices when the head changes
 //   warps 1,8,9 issue the MMAs (54 per tile for a 6 x 11 kernel, split by row tap) into TMEM accumulator n % 2
-//   warps 4-7   epilogue: TMEM -> registers -> 16-bit -> swizzled shared-memory tile -> TMA tiled store (a thread
-//               owns one output row, so direct global stores would touch 32 different lines per instruction)
+//   warps 4-7, 10-13  epilogue (64 columns each): TMEM -> registers -> 16-bit -> swizzled shared-memory tile (double
+//               buffered) -> TMA tiled store (a thread owns one output row, so direct global stores would touch 32
+//               different lines per instruction)
 //
 // MMA schedule.  Staged column sc holds key n0 - 8 + sc; output column x reads staged columns x + a_off + j
 // (a_off = 8 - pad_w).  A k-step is 16 staged columns [16 s, 16 s + 16), s = 0..8; it contributes to the two
@@ -67,11 +68,12 @@ constexpr int TN = 128;            // output columns per tile
 constexpr int NB = TN / 16;        // 16-column blocks
 constexpr int NKS = 9;             // k-steps of 16 staged columns: 8 (left halo) + 128 + 8
 constexpr int NCH = 2 * NKS;       // staged 8-column chunks
-constexpr int NBOX = 3;            // 64-column TMA boxes per staged tile
+constexpr int NBOX = 2;            // 64-column TMA boxes per staged tile (128-byte swizzle); a third box of 16 columns
+                                   // (32-byte swizzle) holds the last k-step
 constexpr int NSTAGE = 3;
 constexpr int OUT_BYTES = 2 * TM * 128;   // output staging: two 64-column boxes of 128 rows x 128 bytes, 128-byte swizzle
 constexpr int NISS = 3;            // MMA-issuing threads (warps 1, 8, 9)
-constexpr int THREADS = 320;
+constexpr int THREADS = 448;       // warps: 0 producer, 1/8/9 MMA issuers, 2-3 tile fix-up, 4-7 and 10-13 epilogue
 
 template <typename T> struct AbFmt;
 template <> struct AbFmt<__nv_bfloat16> { static constexpr int value = 1; };
@@ -136,7 +138,8 @@ struct TileIter {
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS, 1)
-conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my,
+conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mx3,
+                   const __grid_constant__ CUtensorMap my,
                    const void* __restrict__ w, int w_dtype, int y_row0, ConvGeom g, int* err_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -148,9 +151,11 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     const int TH = TM + R - 1;
     const int box_bytes = (TH * 128 + 1023) & ~1023;          // one 64-column box, 1024-byte aligned (swizzle period)
     const int tb_bytes = (R * 1024 * (g.split_w ? 2 : 1) + 1023) & ~1023;   // Toeplitz slices: 32 x 16 per row tap
-    const int stage_bytes = NBOX * box_bytes + tb_bytes;
+    const int box3_bytes = (TH * 32 + 1023) & ~1023;          // the 16-column box: rows of 32 bytes
+    const int tb_off = NBOX * box_bytes + box3_bytes;         // Toeplitz slices follow the boxes
+    const int stage_bytes = tb_off + tb_bytes;
     uint8_t* out_base = smem;                                  // 1024-byte aligned, as the swizzled TMA store needs
-    uint8_t* stage_base = smem + OUT_BYTES;
+    uint8_t* stage_base = smem + 2 * OUT_BYTES;               // two output staging tiles, then the stage ring
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pad_w = (S - 1) / 2;
     const int pad8 = (pad_w + 7) & ~7;
@@ -176,7 +181,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             for (int i = 0; i < 2; ++i) {
                 mbar_init(&acc_full[i], NISS);
                 mbar_init(&init_bar[i], 1);
-                mbar_init(&acc_empty[i], 4);
+                mbar_init(&acc_empty[i], 8);
             }
             fence_mbar_init();
             prefetch_tensormap(&mx);
@@ -187,21 +192,23 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     } else if (warp == 1 && lane == 0) {
         // MMA schedule of one tile, in issue order: batch (row tap i, term) x nine k-steps, even k-steps first (for
         // i = 0 they carry accumulate = 0 and touch every 16-column block exactly once).  Per MMA: A offset and B offset
-        // in 16-byte units from the stage base, accumulator column, flags (bit 0: N = 16, bit 1: accumulate).
+        // in 16-byte units from the stage base, accumulator column, flags (bit 0: N = 16, bit 1: accumulate, bit 2: A in the 32-byte-row box).
         int m = 0;
         for (int i = 0; i < R; ++i)
             for (int part = 0; part < (g.split_w ? 2 : 1); ++part)
                 for (int pass = 0; pass < 2; ++pass)
                     for (int s = pass; s < NKS; s += 2) {
-                        const uint32_t a16 = (uint32_t)(((s / 4) * box_bytes + i * 128 + (s % 4) * 32) >> 4);
+                        // k-steps 0..7 live in the two 128-byte-row boxes, k-step 8 in the 32-byte-row box
+                        const uint32_t a16 = s < 8 ? (uint32_t)(((s / 4) * box_bytes + i * 128 + (s % 4) * 32) >> 4)
+                                                   : (uint32_t)((NBOX * box_bytes + i * 32) >> 4);
                         // Toeplitz slice of row tap i: 32 rows (n') x 16 (kk); the first k-step only touches block 0
                         // (rows 16..31 of the slice, +256 bytes), the last one only block 7 (rows 0..15)
-                        uint32_t b16 = (uint32_t)((NBOX * box_bytes + i * 1024 + part * R * 1024) >> 4);
+                        uint32_t b16 = (uint32_t)((tb_off + i * 1024 + part * R * 1024) >> 4);
                         if (s == 0) b16 += 16;
                         const uint32_t dcol = s == 0 ? 0u : 16u * (uint32_t)(s - 1);
                         const uint32_t n16 = (s == 0 || s == NKS - 1) ? 1u : 0u;
                         const uint32_t acc = (i > 0 || pass > 0 || part > 0) ? 1u : 0u;
-                        sched[m++] = make_uint4(a16, b16, dcol, n16 | (acc << 1));
+                        sched[m++] = make_uint4(a16, b16, dcol, n16 | (acc << 1) | (s == 8 ? 4u : 0u));
                     }
     }
     fence_before_sync();
@@ -221,15 +228,16 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
                 PROF_ACC(0, true)
                 uint8_t* xa = stage_base + st * stage_bytes;
-                mbar_expect_tx(&full_bar[st], (uint32_t)(NBOX * TH * 128));
+                mbar_expect_tx(&full_bar[st], (uint32_t)(NBOX * TH * 128 + TH * 32));
 #pragma unroll
                 for (int j = 0; j < NBOX; ++j)
                     tma_load_3d(xa + j * box_bytes, &mx, &full_bar[st], it.n0() - pad8 + 64 * j, it.m0(g) - (R - 1) - g.x_row0,
                                 it.plane);
+                tma_load_3d(xa + NBOX * box_bytes, &mx3, &full_bar[st], it.n0() - pad8 + 128, it.m0(g) - (R - 1) - g.x_row0, it.plane);
             }
             PROF_FLUSH(12, true)
         }
-    } else if (warp == 1 || warp >= 8) {
+    } else if (warp == 1 || warp == 8 || warp == 9) {
         // ---------------- MMA issuers ----------------
         // Issuing a tcgen05.mma whose descriptors differ from the previous one costs the issuing thread ~100 cycles
         // here (measured), about twice the ~47 cycles the tensor core needs for it, so three threads issue: issuer k
@@ -252,6 +260,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             if (lane == 0) {
                 const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
                 const uint64_t da0 = smem_desc_sw128(xa_addr, 16, 1024);
+                const uint64_t da3 = smem_desc_sw32(xa_addr, 256);           // the last k-step reads the 32-byte-row box
                 const uint64_t db0 = smem_desc_plain(xa_addr, 512, 128);     // k chunks 512 bytes apart, 8-row groups 128
                 const uint32_t d0 = tmem + (uint32_t)(ab * TN);
                 // the nine table entries of a batch are fetched before its MMAs are issued
@@ -261,7 +270,8 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                     for (int j = 0; j < NKS; ++j) e[j] = sched[b * NKS + j];
 #pragma unroll
                     for (int j = 0; j < NKS; ++j)
-                        mma_f16_ss(d0 + e[j].z, da0 + e[j].x, db0 + e[j].y, (e[j].w & 1u) ? idesc16 : idesc32, e[j].w >> 1);
+                        mma_f16_ss(d0 + e[j].z, ((e[j].w & 4u) ? da3 : da0) + e[j].x, db0 + e[j].y, (e[j].w & 1u) ? idesc16 : idesc32,
+                                   (e[j].w >> 1) & 1u);
                     if (b == 0) mbar_arrive(&init_bar[ab]);
                 }
                 mma_commit(&empty_bar[st]);
@@ -285,7 +295,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
             const int head = plane % g.C;
             uint8_t* xa = stage_base + st * stage_bytes;
-            uint8_t* tb = xa + NBOX * box_bytes;
+            uint8_t* tb = xa + tb_off;
             // the stage (and its Toeplitz slices) is free once the MMAs of tile n - NSTAGE are done
             PROF_START
             mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
@@ -324,13 +334,18 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                     if (first < 0) first = 0;
                     int ch = first >> 3;
                     uint8_t* rowp = xa + sr * 128;
+                    // chunk ch of row sr: boxes 0/1 (128-byte rows, chunk index xor row % 8), box 2 (32-byte rows, chunk
+                    // index xor bit 2 of the row: the 32-byte swizzle flips address bit 4 with bit 7)
+                    auto chunk_ptr = [&](int c) -> uint8_t* {
+                        return c < 16 ? rowp + (c >> 3) * box_bytes + (((c & 7) ^ (sr & 7)) << 4)
+                                      : xa + NBOX * box_bytes + sr * 32 + ((((c - 16) ^ (sr >> 2)) & 1) << 4);
+                    };
                     if (first & 7) {
-                        uint16_t* e16 = reinterpret_cast<uint16_t*>(rowp + (ch >> 3) * box_bytes + (((ch & 7) ^ (sr & 7)) << 4));
+                        uint16_t* e16 = reinterpret_cast<uint16_t*>(chunk_ptr(ch));
                         for (int e = first & 7; e < 8; ++e) e16[e] = 0;
                         ++ch;
                     }
-                    for (; ch < NCH; ++ch)
-                        *reinterpret_cast<uint4*>(rowp + (ch >> 3) * box_bytes + (((ch & 7) ^ (sr & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    for (; ch < NCH; ++ch) *reinterpret_cast<uint4*>(chunk_ptr(ch)) = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
             fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
@@ -340,35 +355,37 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         }
         PROF_FLUSH(4, warp == 2)
     } else {
-        // ---------------- epilogue ----------------
-        const int quarter = warp & 3;
+        // ---------------- epilogue: warps 4-7 drain columns 0..63, warps 10-13 columns 64..127 ----------------
+        const int quarter = warp & 3;                        // the TMEM lanes a warp may read depend on its index mod 4
+        const int half = warp >= 10 ? 1 : 0;
         const bool issuer = (warp == 4 && lane == 0);
         const int row = quarter * 32 + lane;                 // row of the tile this thread owns
-        uint8_t* orow = out_base + row * 128;
         PROF_DECL
         TileIter it;
         it.init(g, t_begin);
         for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
             const int ab = n & 1;
             const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
+            uint8_t* obuf = out_base + ab * OUT_BYTES;       // staging tile n % 2: two 64-column boxes
+            uint8_t* orow = obuf + half * (TM * 128) + row * 128;
             PROF_START
             mbar_wait(&acc_full[ab], (n >> 1) & 1, err_flag);
             __syncwarp();
             fence_after_sync();
             PROF_ACC(8, warp == 4)
-            if (issuer) bulk_wait_read();                    // the previous tile's store has finished reading the staging tile
-            named_barrier(1, 128);
+            if (issuer) bulk_wait_read_1();                  // the store of tile n-2 has finished reading this staging tile
+            named_barrier(1, 256);
             PROF_ACC(9, warp == 4)
             const int q = m0 + row;
-#pragma unroll 1
-            for (int cblk = 0; cblk < TN / 32; ++cblk) {
+#pragma unroll
+            for (int cblk = 0; cblk < 2; ++cblk) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TN + cblk * 32), r);
+                tmem_ld_32x32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * TN + half * 64 + cblk * 32), r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int v8 = 0; v8 < 4; ++v8) {
-                    const int col = cblk * 32 + v8 * 8;
-                    const int k = n0 + col;
+                    const int col = cblk * 32 + v8 * 8;      // column inside this warp's 64-column half
+                    const int k = n0 + half * 64 + col;
                     float f[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v8 * 8 + e]);
@@ -382,8 +399,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                     o.y = pack2c<T>(f[2], f[3]);
                     o.z = pack2c<T>(f[4], f[5]);
                     o.w = pack2c<T>(f[6], f[7]);
-                    const int c = (col & 63) >> 3;
-                    *reinterpret_cast<uint4*>(orow + (col >> 6) * (TM * 128) + ((c ^ (row & 7)) << 4)) = o;
+                    *reinterpret_cast<uint4*>(orow + (((col >> 3) ^ (row & 7)) << 4)) = o;
                 }
             }
             fence_before_sync();
@@ -391,11 +407,11 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             if (lane == 0) mbar_arrive(&acc_empty[ab]);
             PROF_ACC(10, warp == 4)
             fence_proxy_async();                             // staging tile written through the generic proxy, read by TMA
-            named_barrier(1, 128);
+            named_barrier(1, 256);
             if (issuer) {
                 // rows past row_end and columns past W are clipped by the tensor map
-                tma_store_3d(&my, out_base, n0, m0 - y_row0, plane);
-                if (n0 + 64 < g.W) tma_store_3d(&my, out_base + TM * 128, n0 + 64, m0 - y_row0, plane);
+                tma_store_3d(&my, obuf, n0, m0 - y_row0, plane);
+                if (n0 + 64 < g.W) tma_store_3d(&my, obuf + TM * 128, n0 + 64, m0 - y_row0, plane);
                 bulk_commit();
             }
             PROF_ACC(11, warp == 4)
@@ -426,7 +442,8 @@ size_t conv2d_tc05_smem_bytes(int R, bool split_w) {
     const int TH = TM + R - 1;
     const size_t box = (size_t)((TH * 128 + 1023) & ~1023);
     const size_t tb = (size_t)((R * 1024 * (split_w ? 2 : 1) + 1023) & ~1023);
-    return 1024 + OUT_BYTES + NSTAGE * (NBOX * box + tb);
+    const size_t box3 = (size_t)((TH * 32 + 1023) & ~1023);
+    return 1024 + 2 * OUT_BYTES + NSTAGE * (NBOX * box + box3 + tb);
 }
 
 template <typename T>
@@ -441,6 +458,10 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
         return rc;
     int* flag = nullptr;
     if ((rc = wait_flag_ptr(&flag))) return rc;
+    CUtensorMap mx3;     // the 16-column box of the last k-step
+    if ((rc = make_tensor_map_3d_mode(&mx3, x, (uint64_t)planes, (uint64_t)x_rows_stored, (uint64_t)W, (uint64_t)xv.width,
+                                      (uint64_t)xv.plane_stride, 16, (uint32_t)TH, 32)))
+        return rc;
     CUtensorMap my;      // rows past row_end are outside this map, so a tile's store never touches them
     if ((rc = make_tensor_map_3d(&my, y, (uint64_t)planes, (uint64_t)(row_end - yv.row0), (uint64_t)W, (uint64_t)yv.width,
                                  (uint64_t)yv.plane_stride, 64, TM, true)))
@@ -465,7 +486,7 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
     MTA_REQUIRE(smem <= 227 * 1024, "conv2d (tcgen05): kernel with %d row taps needs %zu bytes of shared memory", R, smem);
     MTA_CUDA_OK(cudaFuncSetAttribute(conv2d_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const unsigned grid = (unsigned)std::min<long>(g.total_tiles, sms);
-    conv2d_tc05_kernel<T><<<grid, THREADS, smem, st>>>(mx, my, w, w_dtype, yv.row0, g, flag);
+    conv2d_tc05_kernel<T><<<grid, THREADS, smem, st>>>(mx, mx3, my, w, w_dtype, yv.row0, g, flag);
     MTA_LAUNCH_OK("conv2d_tc05_kernel");
 #ifdef MTA_CONV_PROFILE
     if (getenv("MTA_CONV_PROFILE")) {

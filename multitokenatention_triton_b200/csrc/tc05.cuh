@@ -95,6 +95,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
 // All earlier bulk groups of this thread have finished READING shared memory (the source may be overwritten).
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+// At most one of this thread's bulk groups is still reading shared memory (for a double-buffered source).
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory"); }
 // All earlier bulk groups of this thread are complete.
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 // Barrier among `count` threads (a multiple of 32) on hardware barrier `id` (1..15; 0 is __syncthreads).
@@ -127,6 +129,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
     d |= (uint64_t)1 << 46;      // descriptor version for sm_100
     d |= (uint64_t)2 << 61;      // SWIZZLE_128B
+    return d;
+}
+
+// The same for the 32-byte swizzle: K-major rows of 32 bytes (16 elements), sbo = bytes between 8-row groups (256).
+__device__ __forceinline__ uint64_t smem_desc_sw32(uint32_t saddr, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)6 << 61;      // SWIZZLE_32B
     return d;
 }
 
@@ -172,6 +185,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // 3-D map over [planes][rows][cols] of 16-bit elements (cols contiguous, row pitch `row_pitch_elems`, plane pitch
 // `plane_pitch_elems`), box = box_cols x box_rows x 1 plane, with the 128-byte swizzle (box_cols must be 64) or
 // without a swizzle; out-of-bounds reads give zero.
+// As make_tensor_map_3d with the swizzle given in bytes: 0 (none), 32 (box of 16 columns) or 128 (box of 64 columns).
+int make_tensor_map_3d_mode(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
+                            uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_cols, uint32_t box_rows,
+                            int swizzle_bytes);
+
 // Device address of the word that bounded waits raise on timeout (one per device, owned by the library).
 int wait_flag_ptr(int** out);
 
