@@ -127,9 +127,8 @@ int conv2d_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w
     const bool tc05_ok = planes <= 65535 && conv2d_tc05_supported(x, xv, y, yv, W, R, S, dtype, w_dtype);
     MTA_REQUIRE(want != 2 || mma_ok, "conv2d: the mma.sync variant needs a 16-bit dtype, S <= 17, W %% 8 == 0 and 16-byte aligned planes");
     MTA_REQUIRE(want != 3 || tc05_ok, "conv2d: the tcgen05 variant needs a 16-bit dtype, S <= 17, few row taps, W %% 8 == 0 and 16-byte aligned planes");
-    // Measured on the 6 x 11 bf16 case (B4 H16 S2048): mma.sync kernel 274 us, tcgen05 kernel 394 us - the tcgen05
-    // kernel is bound by shared-memory traffic (54 operand fetches of 4 KB per tile), so it is not the default.
-    if (tc05_ok && want == 3)
+    // Measured on the 6 x 11 bf16 case (B4 H16 S2048): tcgen05 kernel 183 us, mma.sync kernel 274 us, CUDA cores 1289 us.
+    if (tc05_ok && (want == 0 || want == 3))
         return conv2d_tc05_launch(x, xv, x_rows_stored, w, w_dtype, y, yv, planes, C, H, W, R, S, causal, row_begin,
                                   row_end, write_upper, dtype, st);
     if (mma_ok && want != 1)

@@ -8,12 +8,14 @@
 //
 // Persistent, warp-specialised kernel: one CTA per SM walks a contiguous range of 128 x 128 output tiles
 // (only tiles that touch keys <= query when causal):
-//   warp 0      TMA producer: two 64-column boxes (128-byte swizzle) and one 16-column box (32-byte swizzle) per tile
+//   warp 0      TMA producer (also stores the zero tiles above the diagonal when the whole output is wanted): two 64-column boxes (128-byte swizzle) and one 16-column box (32-byte swizzle) per tile
 //               bring the (128 + R-1) x 144 halo tile straight into the swizzled K-major layouts the MMA reads (3-stage ring; out-of-range rows / columns arrive as
 //               zero = the conv's zero padding)
-//   warps 2-3   zero the keys above the causal diagonal in the staged tile (diagonal tiles only); rebuild the
+//   warps 2-3, 14-15  zero the keys above the causal diagonal in the staged tile (diagonal tiles only); rebuild the
 //               Toeplitz slices when the head changes
-//   warps 1,8,9 issue the MMAs (54 per tile for a 6 x 11 kernel, split by row tap) into TMEM accumulator n % 2
+//   warps 1,8,9 issue the MMAs into TMEM accumulator n % 2; each issuer owns a fixed set of 16-column output blocks
+//               (3 + 3 + 2), so every output element is accumulated by one thread in program order and the result
+//               does not depend on how the issuers interleave (66 MMAs per tile for a 6 x 11 kernel)
 //   warps 4-7, 10-13  epilogue (64 columns each): TMEM -> registers -> 16-bit -> swizzled shared-memory tile (double
 //               buffered) -> TMA tiled store (a thread owns one output row, so direct global stores would touch 32
 //               different lines per instruction)
@@ -25,8 +27,9 @@
 //       is a function of the shared-memory address alone, so a row tap is just the descriptor's start address
 //       advanced by i * 128 bytes (measured: correct for every i with the base-offset field left at 0);
 //   B = the 32 x 16 Toeplitz slice of row tap i, element (n', kk) = w[i][kk + 16 - n' - a_off] - the same for every s.
-// The first and last k-step touch one block only (N = 16, half of the slice).  For i = 0 the even k-steps go first
-// with accumulate = 0 (they touch every block exactly once), then the odd ones.  Measured: at M = 128 a
+// The first and last k-step touch one block only (N = 16, half of the slice), and so do the k-steps at the edge of
+// an issuer's block range (the neighbouring issuer covers the other half).  For i = 0 an issuer first issues, with
+// accumulate = 0, k-steps that touch each of its blocks exactly once, then the others.  Measured: at M = 128 a
 // tcgen05.mma costs ~44 cycles for any N <= 64, which is why the schedule minimises the MMA count, not the MACs.
 #include <cstdlib>
 
@@ -73,7 +76,10 @@ constexpr int NBOX = 2;            // 64-column TMA boxes per staged tile (128-b
 constexpr int NSTAGE = 3;
 constexpr int OUT_BYTES = 2 * TM * 128;   // output staging: two 64-column boxes of 128 rows x 128 bytes, 128-byte swizzle
 constexpr int NISS = 3;            // MMA-issuing threads (warps 1, 8, 9)
-constexpr int THREADS = 448;       // warps: 0 producer, 1/8/9 MMA issuers, 2-3 tile fix-up, 4-7 and 10-13 epilogue
+constexpr int MAXB = 4;            // MMAs per (row tap, term) of one issuer: its blocks + 1
+// First 16-column output block of issuer k (blocks 0-2, 3-5, 6-7).
+__host__ __device__ constexpr int issuer_block0(int k) { return k == 0 ? 0 : k == 1 ? 3 : k == 2 ? 6 : NB; }
+constexpr int THREADS = 512;       // warps: 0 producer, 1/8/9 MMA issuers, 2-3 and 14-15 tile fix-up, 4-7 and 10-13 epilogue
 
 template <typename T> struct AbFmt;
 template <> struct AbFmt<__nv_bfloat16> { static constexpr int value = 1; };
@@ -103,6 +109,7 @@ __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t saddr, uint32_t lbo
 struct ConvGeom {
     int C, W, R, S, causal, row_begin, row_end, tiles_n, tiles_m, x_row0, write_upper, split_w;
     long tiles_per_plane, total_tiles;
+    long zero_per_plane, zero_total;     // tiles wholly above the diagonal that must be written as zero (write_upper)
 };
 
 // Key tiles that query tile tm reaches.
@@ -143,10 +150,13 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                    const void* __restrict__ w, int w_dtype, int y_row0, ConvGeom g, int* err_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t full_bar[NSTAGE], ready_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2], init_bar[2];
+    __shared__ __align__(8) uint64_t full_bar[NSTAGE], ready_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ uint4 sched[2 * 16 * NKS];      // MMA schedule of one tile (R <= 16 row taps, two terms for fp32 weights)
+    // MMA schedule of one tile per issuer: up to 32 batches (R <= 16 row taps, two terms for fp32 weights) of up to
+    // MAXB MMAs.  x = A offset | B offset << 16 (16-byte units from the stage base), y = accumulator column | flags << 8
+    // (bit 0: N = 16, bit 1: accumulate, bit 2: A in the 32-byte-row box).
+    __shared__ uint2 sched[NISS * 32 * MAXB];
     const int R = g.R, S = g.S;
     const int TH = TM + R - 1;
     const int box_bytes = (TH * 128 + 1023) & ~1023;          // one 64-column box, 1024-byte aligned (swizzle period)
@@ -155,7 +165,8 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     const int tb_off = NBOX * box_bytes + box3_bytes;         // Toeplitz slices follow the boxes
     const int stage_bytes = tb_off + tb_bytes;
     uint8_t* out_base = smem;                                  // 1024-byte aligned, as the swizzled TMA store needs
-    uint8_t* stage_base = smem + 2 * OUT_BYTES;               // two output staging tiles, then the stage ring
+    uint8_t* zero_box = smem + 2 * OUT_BYTES;                 // 16 KB of zeros: source of the zero tiles above the diagonal
+    uint8_t* stage_base = zero_box + TM * 128;                // then the stage ring
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pad_w = (S - 1) / 2;
     const int pad8 = (pad_w + 7) & ~7;
@@ -175,12 +186,11 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         if (lane == 0) {
             for (int i = 0; i < NSTAGE; ++i) {
                 mbar_init(&full_bar[i], 1);
-                mbar_init(&ready_bar[i], 2);
+                mbar_init(&ready_bar[i], 4);
                 mbar_init(&empty_bar[i], NISS);
             }
             for (int i = 0; i < 2; ++i) {
                 mbar_init(&acc_full[i], NISS);
-                mbar_init(&init_bar[i], 1);
                 mbar_init(&acc_empty[i], 8);
             }
             fence_mbar_init();
@@ -189,27 +199,32 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         }
         __syncwarp();
         tmem_alloc(&tmem_slot, 2 * TN);
-    } else if (warp == 1 && lane == 0) {
-        // MMA schedule of one tile, in issue order: batch (row tap i, term) x nine k-steps, even k-steps first (for
-        // i = 0 they carry accumulate = 0 and touch every 16-column block exactly once).  Per MMA: A offset and B offset
-        // in 16-byte units from the stage base, accumulator column, flags (bit 0: N = 16, bit 1: accumulate, bit 2: A in the 32-byte-row box).
-        int m = 0;
+    } else if ((warp == 1 || warp == 8 || warp == 9) && lane == 0) {
+        // This issuer's MMA schedule of one tile, in issue order.  It owns output blocks [b0, b1]; the k-steps that
+        // reach them are b0 .. b1 + 1.  k-step s is an N = 32 MMA onto blocks s-1 and s, except at the two ends of the
+        // range, where only one half of the Toeplitz slice is used (N = 16): rows 16..31 (+256 bytes) onto block b0 for
+        // s = b0, rows 0..15 onto block b1 for s = b1 + 1.  Batch = (row tap i, term); within a batch the k-steps
+        // b0+1, b0+3, ... come first (they touch every owned block exactly once: accumulate = 0 in the first batch).
+        const int issuer = warp == 1 ? 0 : warp - 7;
+        const int b0 = issuer_block0(issuer), b1 = issuer_block0(issuer + 1) - 1;
+        int batch = 0;
         for (int i = 0; i < R; ++i)
-            for (int part = 0; part < (g.split_w ? 2 : 1); ++part)
+            for (int part = 0; part < (g.split_w ? 2 : 1); ++part, ++batch) {
+                int m = 0;
                 for (int pass = 0; pass < 2; ++pass)
-                    for (int s = pass; s < NKS; s += 2) {
+                    for (int s = b0 + 1 - pass; s <= b1 + 1; s += 2) {
                         // k-steps 0..7 live in the two 128-byte-row boxes, k-step 8 in the 32-byte-row box
                         const uint32_t a16 = s < 8 ? (uint32_t)(((s / 4) * box_bytes + i * 128 + (s % 4) * 32) >> 4)
                                                    : (uint32_t)((NBOX * box_bytes + i * 32) >> 4);
-                        // Toeplitz slice of row tap i: 32 rows (n') x 16 (kk); the first k-step only touches block 0
-                        // (rows 16..31 of the slice, +256 bytes), the last one only block 7 (rows 0..15)
                         uint32_t b16 = (uint32_t)((tb_off + i * 1024 + part * R * 1024) >> 4);
-                        if (s == 0) b16 += 16;
-                        const uint32_t dcol = s == 0 ? 0u : 16u * (uint32_t)(s - 1);
-                        const uint32_t n16 = (s == 0 || s == NKS - 1) ? 1u : 0u;
-                        const uint32_t acc = (i > 0 || pass > 0 || part > 0) ? 1u : 0u;
-                        sched[m++] = make_uint4(a16, b16, dcol, n16 | (acc << 1) | (s == 8 ? 4u : 0u));
+                        const bool upper = s == b0, lower = s == b1 + 1;
+                        if (upper) b16 += 16;
+                        const uint32_t dcol = upper ? 16u * (uint32_t)s : 16u * (uint32_t)(s - 1);
+                        const uint32_t acc = (batch > 0 || pass > 0) ? 1u : 0u;
+                        const uint32_t flags = ((upper || lower) ? 1u : 0u) | (acc << 1) | (s == 8 ? 4u : 0u);
+                        sched[(issuer * 32 + batch) * MAXB + m++] = make_uint2(a16 | (b16 << 16), dcol | (flags << 8));
                     }
+            }
     }
     fence_before_sync();
     __syncthreads();
@@ -217,11 +232,35 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     const uint32_t tmem = tmem_slot;
 
     if (warp == 0) {
-        // ---------------- producer ----------------
+        // ---------------- producer (and zero tiles) ----------------
+        // The tiles wholly above the diagonal are part of the output the API returns: they are written as TMA stores of
+        // a zero box, a share of them after every load, so they overlap the compute tiles' traffic.
+        const long active = (g.total_tiles + per - 1) / per;      // CTAs that own compute tiles (the others have returned)
+        const long zper = (g.zero_total + active - 1) / active;
+        const long z_begin = min((long)blockIdx.x * zper, g.zero_total), z_end = min(z_begin + zper, g.zero_total);
+        const long my_zero = z_end - z_begin;
+        if (my_zero > 0) {
+            for (int i = lane; i < TM * 128 / 16; i += 32) reinterpret_cast<uint4*>(zero_box)[i] = make_uint4(0u, 0u, 0u, 0u);
+            fence_proxy_async();
+        }
+        __syncwarp();
         if (lane == 0) {
             PROF_DECL
             TileIter it;
             it.init(g, t_begin);
+            // zero-tile walker: (plane, row tile, column tile) with column tiles conv_key_tiles(tm) .. tiles_n - 1
+            int zp = 0, ztm = 0, ztn = 0;
+            if (my_zero > 0) {
+                zp = (int)(z_begin / g.zero_per_plane);
+                long r = z_begin - (long)zp * g.zero_per_plane;
+                for (ztm = 0;; ++ztm) {
+                    const int nz = g.tiles_n - conv_key_tiles(g, ztm);
+                    if (r < nz) break;
+                    r -= nz;
+                }
+                ztn = conv_key_tiles(g, ztm) + (int)r;
+            }
+            long zi = 0;
             for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
                 const int st = n % NSTAGE;
                 PROF_START
@@ -234,19 +273,34 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                     tma_load_3d(xa + j * box_bytes, &mx, &full_bar[st], it.n0() - pad8 + 64 * j, it.m0(g) - (R - 1) - g.x_row0,
                                 it.plane);
                 tma_load_3d(xa + NBOX * box_bytes, &mx3, &full_bar[st], it.n0() - pad8 + 128, it.m0(g) - (R - 1) - g.x_row0, it.plane);
+                const long z_target = my_zero * (n + 1) / my_tiles;
+                for (; zi < z_target; ++zi) {
+                    const int zm0 = g.row_begin + ztm * TM, zn0 = ztn * TN;
+                    tma_store_3d(&my, zero_box, zn0, zm0 - y_row0, zp);
+                    if (zn0 + 64 < g.W) tma_store_3d(&my, zero_box, zn0 + 64, zm0 - y_row0, zp);
+                    bulk_commit();
+                    if (++ztn == g.tiles_n) {
+                        do {
+                            if (++ztm == g.tiles_m) { ztm = 0; ++zp; }
+                        } while (conv_key_tiles(g, ztm) >= g.tiles_n && zi + 1 < my_zero);
+                        ztn = conv_key_tiles(g, ztm);
+                    }
+                }
             }
+            bulk_wait_all();
             PROF_FLUSH(12, true)
         }
     } else if (warp == 1 || warp == 8 || warp == 9) {
         // ---------------- MMA issuers ----------------
         // Issuing a tcgen05.mma whose descriptors differ from the previous one costs the issuing thread ~100 cycles
-        // here (measured), about twice the ~47 cycles the tensor core needs for it, so three threads issue: issuer k
-        // takes the row taps (and, for fp32 weights, remainder terms) k, k+3, ...  Only the accumulate = 0 MMAs must
-        // come first; they are in batch 0, and issuer 0 releases the others through init_bar once they are issued.
+        // here (measured), about twice the ~47 cycles the tensor core needs for it, so three threads issue, each onto
+        // its own output blocks: no ordering between the issuers is needed, and none affects the result.
         constexpr uint32_t idesc32 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 32);
         constexpr uint32_t idesc16 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 16);
         const int n_batch = R * (g.split_w ? 2 : 1);
         const int issuer = warp == 1 ? 0 : warp - 7;          // 0, 1, 2
+        const int n_mma = issuer_block0(issuer + 1) - issuer_block0(issuer) + 1;     // MMAs per batch
+        const uint2* my_sched = sched + issuer * 32 * MAXB;
         PROF_DECL
         for (int n = 0; n < my_tiles; ++n) {
             const int st = n % NSTAGE, ab = n & 1;
@@ -254,7 +308,6 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             mbar_wait(&ready_bar[st], (n / NSTAGE) & 1, err_flag);
             PROF_ACC(1, true)
             mbar_wait(&acc_empty[ab], ((n >> 1) & 1) ^ 1, err_flag);
-            if (issuer != 0) mbar_wait(&init_bar[ab], (n >> 1) & 1, err_flag);
             PROF_ACC(2, true)
             fence_after_sync();
             if (lane == 0) {
@@ -263,16 +316,18 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 const uint64_t da3 = smem_desc_sw32(xa_addr, 256);           // the last k-step reads the 32-byte-row box
                 const uint64_t db0 = smem_desc_plain(xa_addr, 512, 128);     // k chunks 512 bytes apart, 8-row groups 128
                 const uint32_t d0 = tmem + (uint32_t)(ab * TN);
-                // the nine table entries of a batch are fetched before its MMAs are issued
-                for (int b = issuer; b < n_batch; b += NISS) {
-                    uint4 e[NKS];
+                // the table entries of a batch are fetched before its MMAs are issued
+                for (int b = 0; b < n_batch; ++b) {
+                    uint2 e[MAXB];
 #pragma unroll
-                    for (int j = 0; j < NKS; ++j) e[j] = sched[b * NKS + j];
+                    for (int j = 0; j < MAXB; ++j) e[j] = my_sched[b * MAXB + j];
 #pragma unroll
-                    for (int j = 0; j < NKS; ++j)
-                        mma_f16_ss(d0 + e[j].z, ((e[j].w & 4u) ? da3 : da0) + e[j].x, db0 + e[j].y, (e[j].w & 1u) ? idesc16 : idesc32,
-                                   (e[j].w >> 1) & 1u);
-                    if (b == 0) mbar_arrive(&init_bar[ab]);
+                    for (int j = 0; j < MAXB; ++j)
+                        if (j < n_mma) {
+                            const uint32_t fl = e[j].y >> 8;
+                            mma_f16_ss(d0 + (e[j].y & 0xffu), ((fl & 4u) ? da3 : da0) + (e[j].x & 0xffffu), db0 + (e[j].x >> 16),
+                                       (fl & 1u) ? idesc16 : idesc32, (fl >> 1) & 1u);
+                        }
                 }
                 mma_commit(&empty_bar[st]);
                 mma_commit(&acc_full[ab]);
@@ -281,15 +336,13 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             PROF_ACC(3, true)
         }
         PROF_FLUSH(0, warp == 1)
-    } else if (warp < 4) {
-        // ---------------- (warps 2-3) causal zeroing of the staged tile, Toeplitz slices ----------------
-        const int ft = tid - 64;          // 0..63
+    } else if (warp < 4 || warp >= 14) {
+        // ---------------- (warps 2-3, 14-15) causal zeroing of the staged tile, Toeplitz slices ----------------
+        const int ft = warp < 4 ? tid - 64 : tid - 448 + 64;     // 0..127
         TileIter it;
         it.init(g, t_begin);
-        int prev_head[NSTAGE];
+        int ph0 = -1, ph1 = -1, ph2 = -1;                 // head whose Toeplitz slices each stage holds (NSTAGE == 3)
         PROF_DECL
-#pragma unroll
-        for (int i = 0; i < NSTAGE; ++i) prev_head[i] = -1;
         for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
             const int st = n % NSTAGE;
             const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
@@ -300,15 +353,15 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             PROF_START
             mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
             PROF_ACC(4, warp == 2)
-            int ph = -1;
-#pragma unroll
-            for (int i = 0; i < NSTAGE; ++i)
-                if (i == st) { ph = prev_head[i]; prev_head[i] = head; }
+            int ph;
+            if (st == 0) { ph = ph0; ph0 = head; }
+            else if (st == 1) { ph = ph1; ph1 = head; }
+            else { ph = ph2; ph2 = head; }
             if (ph != head) {
                 // slice of row tap i, element (n', kk) = w[i][kk + 16 - n' - a_off]; no-swizzle K-major layout:
                 // 8 rows x 16 bytes per core matrix, the two k chunks 512 bytes apart, row groups 128 bytes apart
                 const int total = R * 512;
-                for (int idx = ft; idx < total; idx += 64) {
+                for (int idx = ft; idx < total; idx += 128) {
                     const int i = idx / 512, e = idx % 512;
                     const int nn = e / 16, kk = e % 16;
                     const int j = kk + 16 - nn - a_off;
@@ -327,7 +380,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             if (g.causal && n0 - pad8 + NCH * 8 - 1 > m0 - (R - 1)) {
                 // one thread per staged row: zero from the first key above the query to the end of the row
                 const int c0 = n0 - pad8;
-                for (int sr = ft; sr < TH; sr += 64) {
+                for (int sr = ft; sr < TH; sr += 128) {
                     const int qq = m0 - (R - 1) + sr;
                     int first = qq - c0 + 1;                      // first staged column to zero
                     if (first >= NCH * 8) continue;
@@ -424,26 +477,12 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     if (warp == 0) tmem_dealloc(tmem, 2 * TN);
 }
 
-// Zero fill of the key tiles that lie entirely above the diagonal (what the conv kernel never visits).
-template <typename T>
-__global__ void __launch_bounds__(256)
-fill_above_kernel(T* __restrict__ y, PlaneView yv, int W, int row_begin, int row_end) {
-    const long plane = blockIdx.y;
-    const int q = row_begin + (int)blockIdx.x;
-    if (q >= row_end) return;
-    const int tm = (q - row_begin) / TM;
-    const int q_last = min(row_begin + (tm + 1) * TM, row_end);
-    const int k_start = min(((q_last + TN - 1) / TN) * TN, W);      // first key the conv tiles of this row do not cover
-    uint4* row = reinterpret_cast<uint4*>(y + plane * yv.plane_stride + (long)(q - yv.row0) * yv.width);
-    for (int ch = k_start / 8 + threadIdx.x; ch < W / 8; ch += 256) row[ch] = make_uint4(0u, 0u, 0u, 0u);
-}
-
 size_t conv2d_tc05_smem_bytes(int R, bool split_w) {
     const int TH = TM + R - 1;
     const size_t box = (size_t)((TH * 128 + 1023) & ~1023);
     const size_t tb = (size_t)((R * 1024 * (split_w ? 2 : 1) + 1023) & ~1023);
     const size_t box3 = (size_t)((TH * 32 + 1023) & ~1023);
-    return 1024 + 2 * OUT_BYTES + NSTAGE * (NBOX * box + box3 + tb);
+    return 1024 + 2 * OUT_BYTES + TM * 128 + NSTAGE * (NBOX * box + box3 + tb);
 }
 
 template <typename T>
@@ -479,6 +518,8 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
     }
     g.tiles_per_plane = per_plane;
     g.total_tiles = per_plane * planes;
+    g.zero_per_plane = (causal && write_upper) ? (long)tiles_m * g.tiles_n - per_plane : 0;
+    g.zero_total = g.zero_per_plane * planes;
     int dev = 0, sms = 0;
     MTA_CUDA_OK(cudaGetDevice(&dev));
     MTA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -501,11 +542,6 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
                 h[10] / n0, h[11] / n0);
     }
 #endif
-    if (causal && write_upper && W > TN) {
-        dim3 fgrid((unsigned)(row_end - row_begin), (unsigned)planes);
-        fill_above_kernel<T><<<fgrid, 256, 0, st>>>(static_cast<T*>(y), yv, W, row_begin, row_end);
-        MTA_LAUNCH_OK("fill_above_kernel");
-    }
     return MTA_OK;
 }
 
