@@ -64,6 +64,16 @@ int mta_head_linear_fwd(const void* x, const void* Wm, void* y, int N, int C, in
 int mta_softmax_fwd(const void* x, void* y, int N, int C, int P, int Q, int causal, int dtype, void* stream);
 
 /*
+ * Causal head mix followed by the row softmax of the mixed logits, in one pass over the planes:
+ *   y[n,o,p,q] = softmax_q( sum_h Wm[o,h] * x[n,h,p,q] over q <= p ),  0 for q > p.
+ * The mixed logits are rounded to the dtype of x before the softmax, as the two reference stages do
+ * (head mix with output_value = -inf, then F.softmax(scores.float(), -1).type_as(xq):
+ * mta_attention_triton.py:76-79).  x, y: (N,C,P,Q) contiguous, x != y; Wm: (C,C).
+ */
+int mta_head_linear_softmax_fwd(const void* x, const void* Wm, void* y, int N, int C, int P, int Q, int x_dtype,
+                                int w_dtype, void* stream);
+
+/*
  * Scaled scores Q K^T * scale for keys k <= q (entries above the diagonal are never written when
  * causal) and P V over keys k <= q.  They stand in for the two torch.matmul calls of
  * MTAAttentionTriton.forward (mta_attention_triton.py:68-71, :89).  q,k,v,o: (B,H,S,D); s,p: (B,H,S,S).
@@ -132,8 +142,9 @@ void mta_reset_launch_count(void);
 
 /* Selects implementation variants for A/B measurement: key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core;
  * key "conv2d" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core, 3 tcgen05 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core,
- * 2 tcgen05 tensor-core; key "fused" (mta_fused_fwd) -> 0 auto, 1 one kernel per stage, 2 fused conv + head-mix stages with the
- * softmax folded in (16-bit dtypes, H <= 16).  Returns 0, or 1 for an unknown key/value. */
+ * 2 tcgen05 tensor-core; key "fused" (mta_fused_fwd) -> 0 auto (one kernel per stage, the first head mix and the
+ * softmax as one kernel), 1 strictly one kernel per stage, 2 fused conv + head-mix stages with the softmax folded in (16-bit
+ * dtypes, H <= 16).  Returns 0, or 1 for an unknown key/value. */
 int mta_set_variant(const char* key, int value);
 
 #ifdef __cplusplus

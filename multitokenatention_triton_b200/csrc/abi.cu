@@ -110,6 +110,24 @@ int mta_softmax_fwd(const void* x, void* y, int N, int C, int P, int Q, int caus
                           static_cast<cudaStream_t>(stream));
 }
 
+int mta_head_linear_softmax_fwd(const void* x, const void* Wm, void* y, int N, int C, int P, int Q, int x_dtype, int w_dtype,
+                                void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(x_dtype) && dtype_ok(w_dtype), "head_linear_softmax: unknown dtype code (x %d, w %d)", x_dtype, w_dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && P >= 0 && Q >= 0, "head_linear_softmax: bad shape N=%d C=%d P=%d Q=%d", N, C, P, Q);
+    if ((long)N * P * Q == 0) return MTA_OK;
+    MTA_REQUIRE(x && Wm && y, "head_linear_softmax: null pointer");
+    MTA_REQUIRE(x != y, "head_linear_softmax: in-place operation is not supported");
+    if (int rc = check_device()) return rc;
+    const PlaneView v = full_view(P, Q);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (variant("fused") != 1 && head_mix_softmax_supported(x, v, y, v, C, Q, 1, x_dtype))
+        return head_mix_softmax_launch(x, v, Wm, w_dtype, y, v, N, C, Q, 0, P, true, x_dtype, st);
+    // shapes the one-pass kernel does not take: the two stages, the softmax in place
+    if (int rc = head_linear_launch(x, v, Wm, w_dtype, y, v, N, C, P, Q, 1, 0.0f, 0, P, false, x_dtype, st)) return rc;
+    return softmax_launch(y, v, y, v, (long)N * C, P, Q, 1, 0, P, true, 1.0f, x_dtype, st);
+}
+
 int mta_qk_scores_fwd(const void* q, const void* k, void* s, int B, int H, int S, int D, float scale, int round_scale,
                       int causal, int dtype, void* stream) {
     g_error[0] = 0;

@@ -103,8 +103,13 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
         return pv_launch(bufA, pv, nrows, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st);
     }
     if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
-    if ((rc = head_linear_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.rb, pl.r1, false, dtype, st))) return rc;
-    if ((rc = softmax_launch(bufA, pv, bufA, pv, planes, S, S, causal, pl.rb, pl.r1, false, 1.0f, dtype, st))) return rc;
+    // the first head mix and the softmax run as one kernel where it applies (mta_set_variant("fused", 1) keeps them apart)
+    if (variant("fused") != 1 && head_mix_softmax_supported(bufB, pv, bufA, pv, H, S, causal, dtype)) {
+        if ((rc = head_mix_softmax_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, pl.rb, pl.r1, false, dtype, st))) return rc;
+    } else {
+        if ((rc = head_linear_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.rb, pl.r1, false, dtype, st))) return rc;
+        if ((rc = softmax_launch(bufA, pv, bufA, pv, planes, S, S, causal, pl.rb, pl.r1, false, 1.0f, dtype, st))) return rc;
+    }
     if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w2, w_dtype, bufB, pv, planes, H, S, S, cq2, ck2, causal, pl.r0, pl.r1, !causal, dtype, st))) return rc;
     if ((rc = head_linear_launch(bufB, pv, W2, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.r0, pl.r1, false, dtype, st))) return rc;
     return pv_launch(bufA, pv, pl.r1 - pl.ra, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st);

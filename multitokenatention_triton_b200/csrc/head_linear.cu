@@ -81,6 +81,24 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
     return *reinterpret_cast<uint32_t*>(&r);
 }
 
+// 32-byte global accesses (sm_100): a lane of the tensor-core kernels owns 16 consecutive keys of a head, and two
+// separate 16-byte stores would each write half of a 32-byte sector.
+__device__ __forceinline__ void st_global_v8(void* p, const uint4& a, const uint4& b) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+__device__ __forceinline__ void ld_global_v8(const void* p, uint4& a, uint4& b) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+                 : "l"(p)
+                 : "memory");
+}
+// Rows of a view start on 32-byte boundaries (so 16 keys from a multiple of 16 are one aligned 32-byte piece).
+__host__ __device__ inline bool rows_aligned32(const void* p, const PlaneView& v) {
+    return (reinterpret_cast<uintptr_t>(p) & 31u) == 0 && v.width % 16 == 0 && v.plane_stride % 16 == 0;
+}
+
 constexpr int MMA_WARPS = 4;                // warps per CTA
 constexpr int MMA_KEYS_PER_WARP = 64;       // keys of one row handled per warp step
 
@@ -209,6 +227,368 @@ head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __rest
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Head mix followed by the causal row softmax, in one kernel (16-bit dtypes, causal):
+//   y[n,o,p,:p+1] = softmax_k( round16( sum_h Wm[o,h] * x[n,h,p,k] ) ),   entries k > p are written as 0 (write_upper)
+//   or left untouched.
+// Stands in for the reference's head mix with fill -inf followed by F.softmax(scores.float(), -1).type_as(xq)
+// (mta_attention_triton.py:76-79) without the extra pass over the score planes that a separate softmax costs.
+//
+// A CTA owns one (n, p): all heads of one query row.  Phase 1 walks the row in blocks of 64 keys per warp exactly as
+// head_linear_mma_kernel does, rounds the mixed logits to the 16-bit dtype (the reference's rounding point), writes
+// them to y and keeps a running (max, sum of exponentials) per output head.  The per-head statistics are combined
+// across the CTA in a fixed order, and in phase 2 every thread re-reads the vectors it wrote itself (they are still in
+// L2), turns them into probabilities and writes them back.  Rows are handed out longest first.
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// (m, s) <- combination of two partial softmax statistics; m = -inf marks an empty part.
+__device__ __forceinline__ void stat_merge(float& m, float& s, float m2, float s2) {
+    const float mn = fmaxf(m, m2);
+    if (mn == -INFINITY) { s = 0.0f; return; }
+    s = s * ex2f((m - mn) * LOG2E) + s2 * ex2f((m2 - mn) * LOG2E);
+    m = mn;
+}
+
+constexpr int MS_DEPTH = 4;        // ring slots per warp: loads run three 64-key blocks ahead
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int n = valid ? 16 : 0;                  // 0 source bytes: the 16 destination bytes are zero filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Packed maximum of the two 16-bit values of each operand word.
+template <typename T> __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t max2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t max2<__half>(uint32_t a, uint32_t b) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+// The two 16-bit values of a word as floats.
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+}
+
+// d = a * b (no accumulator input: saves zeroing the accumulators of every key block).
+__device__ __forceinline__ void mma_tf32_m16n8k8_first(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+template <typename T, int CP, bool SPLITW, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 4)
+head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype, T* y,
+                        PlaneView yv, int C, int Q, int row_end, int write_upper) {
+    constexpr int KSTEPS = CP / 8;
+    constexpr int MT = (CP + 15) / 16;
+    constexpr int NLOAD = CP / 4;
+    constexpr int KB = MMA_KEYS_PER_WARP;
+    __shared__ float red_m[WARPS][MT * 16], red_s[WARPS][MT * 16];
+    extern __shared__ uint4 ms_ring[];                     // [warp][MS_DEPTH][NLOAD][lane]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const long n = blockIdx.y;
+    const int p = row_end - 1 - (int)blockIdx.x;           // longest rows first
+    const int n_keys = min(p + 1, Q);
+    const int nblk = (n_keys + KB - 1) / KB;
+    const bool wide = rows_aligned32(y, yv);
+    // key blocks wholly below the diagonal take the short path when every MMA row and column is a real head
+    const bool fast = wide && C == CP && C == 16 * MT;
+
+    uint32_t wa[MT][KSTEPS][4];
+    uint32_t wl[SPLITW ? MT : 1][SPLITW ? KSTEPS : 1][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int o = 16 * mt + g + ((r & 1) ? 8 : 0);
+                const int h = 8 * ks + t + ((r & 2) ? 4 : 0);
+                const float v = (o < C && h < C) ? load_weight(Wm, (long)o * C + h, w_dtype) : 0.0f;
+                if (SPLITW) {
+                    const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
+                    wa[mt][ks][r] = hi;
+                    wl[SPLITW ? mt : 0][SPLITW ? ks : 0][r] = __float_as_uint(v - __uint_as_float(hi));
+                } else {
+                    wa[mt][ks][r] = __float_as_uint(v);
+                }
+            }
+
+    // Lane (g,t) reads keys [8g, 8g+8) of every 64-key block of heads t, t+4, ... and owns keys [16t, 16t+16) of
+    // output heads g, g+8 (+16 per further 16-row MMA tile): row pointers at those offsets, once per row.
+    const T* xin[NLOAD];
+#pragma unroll
+    for (int j = 0; j < NLOAD; ++j) xin[j] = x + xv.at(n * C + min(t + 4 * j, C - 1), p, 8 * g);
+    T* yout[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) yout[mt][hh] = y + yv.at(n * C + min(16 * mt + g + 8 * hh, C - 1), p, 16 * t);
+
+    float rm[MT][2], rs[MT][2];                            // running statistics of output heads 16 mt + g + 8 hh
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) { rm[mt][0] = rm[mt][1] = -INFINITY; rs[mt][0] = rs[mt][1] = 0.0f; }
+
+    // The loads run MS_DEPTH - 1 blocks ahead as asynchronous copies into a ring in shared memory; a lane only ever
+    // reads the slots it filled itself, so waiting for its own copy groups is all the synchronisation the ring needs.
+    uint4* ring = ms_ring + (size_t)warp * MS_DEPTH * NLOAD * 32 + lane;
+    auto issue_block = [&](int blk, int slot) {
+        const bool in_ok = blk < nblk && blk * KB + 8 * g < n_keys;
+#pragma unroll
+        for (int j = 0; j < NLOAD; ++j) {
+            const bool ok = in_ok && t + 4 * j < C;
+            cp_async16(ring + (slot * NLOAD + j) * 32, ok ? xin[j] + blk * KB : x, ok);       // zero fill when not ok
+        }
+        cp_async_commit();
+    };
+
+    // ---- phase 1: mix, round, write the logits, running statistics ----
+#pragma unroll
+    for (int d = 0; d < MS_DEPTH - 1; ++d) issue_block(warp + d * WARPS, d);
+    int it = 0;
+#pragma unroll 1
+    for (int blk = warp; blk < nblk; blk += WARPS, ++it) {
+        const int key0 = blk * KB;
+        issue_block(blk + (MS_DEPTH - 1) * WARPS, (it + MS_DEPTH - 1) % MS_DEPTH);
+        cp_async_wait<MS_DEPTH - 1>();                                  // this block's group has landed
+        uint4 xr[NLOAD];
+#pragma unroll
+        for (int j = 0; j < NLOAD; ++j) xr[j] = ring[((it % MS_DEPTH) * NLOAD + j) * 32];
+        float acc[8][MT][4];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS; ++ks) {
+                    const uint32_t b0 = elem_bits<T>(xr[2 * ks], e), b1 = elem_bits<T>(xr[2 * ks + 1], e);
+                    if (SPLITW) {
+                        if (ks == 0) mma_tf32_m16n8k8_first(acc[e][mt], wl[SPLITW ? mt : 0][SPLITW ? ks : 0], b0, b1);
+                        else mma_tf32_m16n8k8(acc[e][mt], wl[SPLITW ? mt : 0][SPLITW ? ks : 0], b0, b1);
+                        mma_tf32_m16n8k8(acc[e][mt], wa[mt][ks], b0, b1);
+                    } else {
+                        if (ks == 0) mma_tf32_m16n8k8_first(acc[e][mt], wa[mt][ks], b0, b1);
+                        else mma_tf32_m16n8k8(acc[e][mt], wa[mt][ks], b0, b1);
+                    }
+                }
+            }
+        // c0 / c1 of MMA e = 0..7 are keys key0 + 16t + e / + 8 + e of head g, c2 / c3 the same keys of head g + 8
+        const bool full = fast && key0 + KB <= n_keys;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                // the lane's 16 keys rounded to the 16-bit dtype: word i of pk[cc] holds keys 8 cc + 2 i, + 1
+                uint4 pk[2];
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    pk[cc].x = pack2<T>(acc[0][mt][2 * hh + cc], acc[1][mt][2 * hh + cc]);
+                    pk[cc].y = pack2<T>(acc[2][mt][2 * hh + cc], acc[3][mt][2 * hh + cc]);
+                    pk[cc].z = pack2<T>(acc[4][mt][2 * hh + cc], acc[5][mt][2 * hh + cc]);
+                    pk[cc].w = pack2<T>(acc[6][mt][2 * hh + cc], acc[7][mt][2 * hh + cc]);
+                }
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    unpack2<T>((&pk[0].x)[i], v[2 * i], v[2 * i + 1]);
+                    unpack2<T>((&pk[1].x)[i], v[8 + 2 * i], v[8 + 2 * i + 1]);
+                }
+                if (full) {
+                    uint32_t m2 = max2<T>(max2<T>(max2<T>(pk[0].x, pk[0].y), max2<T>(pk[0].z, pk[0].w)),
+                                          max2<T>(max2<T>(pk[1].x, pk[1].y), max2<T>(pk[1].z, pk[1].w)));
+                    float mlo, mhi;
+                    unpack2<T>(m2, mlo, mhi);
+                    const float m_new = fmaxf(rm[mt][hh], fmaxf(mlo, mhi));
+                    const float mlog = m_new * LOG2E;
+                    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        s0 += ex2f(fmaf(v[i], LOG2E, -mlog));
+                        s1 += ex2f(fmaf(v[i + 1], LOG2E, -mlog));
+                    }
+                    rs[mt][hh] = fmaf(rs[mt][hh], ex2f((rm[mt][hh] - m_new) * LOG2E), s0 + s1);
+                    rm[mt][hh] = m_new;
+                    st_global_v8(yout[mt][hh] + key0, pk[0], pk[1]);
+                    continue;
+                }
+                // block on the diagonal (or a shape the short path does not take): keys past the diagonal are masked
+                const int o = 16 * mt + g + 8 * hh;
+                if (o >= C) continue;
+                const int k16 = key0 + 16 * t;
+                float lmax = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (k16 + i >= n_keys) v[i] = -INFINITY;
+                    lmax = fmaxf(lmax, v[i]);
+                }
+                const float m_new = fmaxf(rm[mt][hh], lmax);
+                if (m_new != -INFINITY) {
+                    const float mlog = m_new * LOG2E;
+                    float ssum = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) ssum += ex2f(fmaf(v[i], LOG2E, -mlog));
+                    rs[mt][hh] = rs[mt][hh] * ex2f((rm[mt][hh] - m_new) * LOG2E) + ssum;
+                    rm[mt][hh] = m_new;
+                }
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int kq = k16 + 8 * cc;
+                    if (kq >= n_keys) continue;
+                    T* dst = yout[mt][hh] + key0 + 8 * cc;
+                    if (kq + 8 <= n_keys) {
+                        *reinterpret_cast<uint4*>(dst) = pk[cc];
+                    } else {                                   // the vector that holds the diagonal: keys past it stay untouched
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (kq + e < n_keys) dst[e] = from_f32<T>(v[8 * cc + e]);
+                    }
+                }
+            }
+    }
+    cp_async_wait<0>();
+
+    // ---- statistics of the whole row: the four lanes of a head, then the warps, in a fixed order ----
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float m = rm[mt][hh], s = rs[mt][hh];
+#pragma unroll
+            for (int off = 1; off <= 2; off <<= 1) {
+                const float m2 = __shfl_xor_sync(0xffffffffu, m, off), s2 = __shfl_xor_sync(0xffffffffu, s, off);
+                stat_merge(m, s, m2, s2);
+            }
+            if (t == 0) { red_m[warp][16 * mt + g + 8 * hh] = m; red_s[warp][16 * mt + g + 8 * hh] = s; }
+        }
+    __syncthreads();
+    // p = 2^(x log2e - shift), shift = max log2e + log2(sum): the division by the sum is folded into the exponent
+    float shift[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int o = 16 * mt + g + 8 * hh;
+            float m = red_m[0][o], s = red_s[0][o];
+#pragma unroll
+            for (int w = 1; w < WARPS; ++w) stat_merge(m, s, red_m[w][o], red_s[w][o]);
+            shift[mt][hh] = fmaf(m, LOG2E, log2f(s));
+        }
+
+    // ---- phase 2: every thread turns the logits it wrote into probabilities (two blocks per step: the loads of
+    // both are in flight together) ----
+    auto to_prob = [&](uint4& r, float sh) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            unpack2<T>((&r.x)[i], lo, hi);
+            (&r.x)[i] = pack2<T>(ex2f(fmaf(lo, LOG2E, -sh)), ex2f(fmaf(hi, LOG2E, -sh)));
+        }
+    };
+#pragma unroll 1
+    for (int blk = warp; blk < nblk; blk += 2 * WARPS) {
+        const int key0 = blk * KB;
+        uint4 raw[2][MT][2][2];
+        if (fast && key0 + (WARPS + 1) * KB <= n_keys) {   // both blocks wholly below the diagonal
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh)
+                        ld_global_v8(yout[mt][hh] + key0 + u * WARPS * KB, raw[u][mt][hh][0], raw[u][mt][hh][1]);
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        to_prob(raw[u][mt][hh][0], shift[mt][hh]);
+                        to_prob(raw[u][mt][hh][1], shift[mt][hh]);
+                        st_global_v8(yout[mt][hh] + key0 + u * WARPS * KB, raw[u][mt][hh][0], raw[u][mt][hh][1]);
+                    }
+            continue;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int o = 16 * mt + g + 8 * hh;
+                    const int k16 = key0 + u * WARPS * KB + 16 * t;
+                    if (o >= C) continue;
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int kq = k16 + 8 * cc;
+                        if (kq >= n_keys) continue;
+                        T* dst = yout[mt][hh] + key0 + u * WARPS * KB + 8 * cc;
+                        if (kq + 8 <= n_keys) {
+                            uint4 r = *reinterpret_cast<const uint4*>(dst);
+                            to_prob(r, shift[mt][hh]);
+                            *reinterpret_cast<uint4*>(dst) = r;
+                        } else {                               // the vector that holds the diagonal
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                if (kq + e < n_keys)
+                                    dst[e] = from_f32<T>(ex2f(fmaf(to_f32<T>(dst[e]), LOG2E, -shift[mt][hh])));
+                                else if (write_upper)
+                                    dst[e] = from_f32<T>(0.0f);
+                            }
+                        }
+                    }
+                }
+    }
+    if (write_upper) {                                     // probabilities above the diagonal are exactly 0
+        const int v0 = (n_keys + 7) >> 3, nv = Q >> 3;
+        for (int o = 0; o < C; ++o) {
+            uint4* row = reinterpret_cast<uint4*>(y + yv.at(n * C + o, p, 0));
+            for (int i = v0 + (int)threadIdx.x; i < nv; i += WARPS * 32) row[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+}
+
+
+template <typename T, int CP>
+int launch_mix_softmax(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
+                       int row_begin, int row_end, bool write_upper, cudaStream_t st) {
+    constexpr int WARPS = 4;
+    dim3 grid((unsigned)(row_end - row_begin), (unsigned)N);
+    const size_t smem = (size_t)WARPS * MS_DEPTH * (CP / 4) * 32 * sizeof(uint4);
+    if (smem > 48 * 1024) {
+        MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_softmax_kernel<T, CP, true, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_softmax_kernel<T, CP, false, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    if (w_dtype == MTA_F32)
+        head_mix_softmax_kernel<T, CP, true, WARPS><<<grid, WARPS * 32, smem, st>>>(static_cast<const T*>(x), xv, Wm, w_dtype,
+                                                                               static_cast<T*>(y), yv, C, Q, row_end, write_upper ? 1 : 0);
+    else
+        head_mix_softmax_kernel<T, CP, false, WARPS><<<grid, WARPS * 32, smem, st>>>(static_cast<const T*>(x), xv, Wm, w_dtype,
+                                                                                static_cast<T*>(y), yv, C, Q, row_end, write_upper ? 1 : 0);
+    MTA_LAUNCH_OK("head_mix_softmax_kernel");
+    return MTA_OK;
+}
+
 template <typename T, int CP>
 int launch_simt(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
                 int causal, float fill, int row_begin, int row_end, bool write_upper, cudaStream_t st) {
@@ -270,6 +650,28 @@ bool vector_ok(const void* p, PlaneView v) {
 }
 
 }  // namespace
+
+bool head_mix_softmax_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype) {
+    return causal && dtype != MTA_F32 && C <= 32 && Q % 8 == 0 && x != y && vector_ok(x, xv) && vector_ok(y, yv);
+}
+
+int head_mix_softmax_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C,
+                            int Q, int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st) {
+    if (N == 0 || row_end <= row_begin || Q == 0) return MTA_OK;
+    MTA_REQUIRE(head_mix_softmax_supported(x, xv, y, yv, C, Q, 1, dtype),
+                "head_mix_softmax: needs a 16-bit dtype, C <= 32, Q %% 8 == 0, 16-byte aligned rows and x != y");
+    MTA_REQUIRE(N <= 65535, "head_mix_softmax: N = %d exceeds 65535", N);
+#define MTA_MS_CASE(TV, CPV) return launch_mix_softmax<TV, CPV>(x, xv, Wm, w_dtype, y, yv, N, C, Q, row_begin, row_end, write_upper, st)
+    if (dtype == MTA_BF16) {
+        if (C <= 8) MTA_MS_CASE(__nv_bfloat16, 8);
+        if (C <= 16) MTA_MS_CASE(__nv_bfloat16, 16);
+        MTA_MS_CASE(__nv_bfloat16, 32);
+    }
+    if (C <= 8) MTA_MS_CASE(__half, 8);
+    if (C <= 16) MTA_MS_CASE(__half, 16);
+    MTA_MS_CASE(__half, 32);
+#undef MTA_MS_CASE
+}
 
 int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C,
                        int P, int Q, int causal, float fill, int row_begin, int row_end, bool write_upper, int dtype,

@@ -24,6 +24,12 @@ int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype,
                        int C, int P, int Q, int causal, float fill, int row_begin, int row_end, bool write_upper,
                        int dtype, cudaStream_t st);
 
+// Head mix followed by the causal row softmax of the mixed logits, in one pass (16-bit dtypes, C <= 32, causal);
+// entries above the diagonal of y are written as 0 when `write_upper`, else left untouched.
+bool head_mix_softmax_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype);
+int head_mix_softmax_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C,
+                            int Q, int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st);
+
 // Causal row softmax of pre_scale * x; rows [row_begin,row_end).
 int softmax_launch(const void* x, PlaneView xv, void* y, PlaneView yv, long planes, int P, int Q, int causal,
                    int row_begin, int row_end, bool write_upper, float pre_scale, int dtype, cudaStream_t st);

@@ -1,6 +1,6 @@
 """Micro-benchmarks of the stand-alone kernels on the configurations their roofline targets are quoted on.
 
-    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|qk|pv|all] [--variant V]
+    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|mix_softmax|qk|pv|all] [--variant V]
                                                         [--batch N] [--seq S] [--iters K]
 
   conv2d       causal depthwise conv 6x11 on a (B=4, H=16, S=2048, S) bf16 score plane
@@ -63,7 +63,7 @@ def _line(name, ms, nbytes=None, flops=None, **extra):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "qk", "pv", "all"])
+    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "mix_softmax", "qk", "pv", "all"])
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--heads", type=int, default=16)
@@ -93,11 +93,11 @@ def main():
         _line("conv2d 6x11 causal", ms, nbytes=es * N * C * (tri + S * S), shape=shape, variant=a.variant,
               lower_only_bytes=2 * es * N * C * tri)
         del x, y
-    if a.which in ("head_linear", "softmax", "all"):
+    if a.which in ("head_linear", "softmax", "mix_softmax", "all"):
         inp = make_head_linear_inputs(N, C, S, dtype, seed=2)
         x, W = inp["x"].to(dev), inp["W"].to(dev)
         y = torch.empty_like(x)
-        if a.which != "softmax":
+        if a.which in ("head_linear", "all"):
             for fill in (0.0, float("-inf")):
                 def run():
                     _lib.check(_lib.lib().mta_head_linear_fwd(x.data_ptr(), W.data_ptr(), y.data_ptr(), N, C, S, S, 1, fill,
@@ -109,6 +109,13 @@ def main():
         if a.which in ("softmax", "all"):
             ms = _time(lambda: ops.softmax_fwd(x, True, out=y), a.iters)
             _line("softmax causal rows", ms, nbytes=es * N * C * (tri + S * S), shape=shape)
+        if a.which in ("mix_softmax", "all"):
+            def run():
+                _lib.check(_lib.lib().mta_head_linear_softmax_fwd(x.data_ptr(), W.data_ptr(), y.data_ptr(), N, C, S, S,
+                                                                  _lib.dtype_code(x), _lib.dtype_code(W), _lib.stream_ptr(dev)),
+                           "head_linear_softmax")
+            ms = _time(run, a.iters)
+            _line(f"head mix {C}x{C} + softmax, one pass", ms, nbytes=es * N * C * (tri + S * S), shape=shape)
         del x, y
     if a.which in ("qk", "pv", "all"):
         g = torch.Generator().manual_seed(3)

@@ -60,6 +60,23 @@ def head_linear_fwd(x: torch.Tensor, weight: torch.Tensor, causal: bool = True, 
     return y
 
 
+def head_linear_softmax_fwd(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Causal head mix then row softmax of the mixed logits in one pass: x (N,C,P,Q), weight (C,C) -> probabilities
+    (N,C,P,Q), zero above the diagonal.  Equals softmax_fwd(head_linear_fwd(x, weight, True, -inf)) up to the order of
+    the fp32 sums."""
+    x = _cuda_contig(x, "input")
+    if x.dim() != 4:
+        raise MTALibraryError(f"head_linear_softmax: expected input (N,C,P,Q), got {tuple(x.shape)}")
+    N, C, P, Q = x.shape
+    assert weight.shape == (C, C), f"Weight must be a ({C},{C}) matrix, got {tuple(weight.shape)}"
+    w = _weight(weight, x, "weight")
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(lib().mta_head_linear_softmax_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), N, C, P, Q, dtype_code(x),
+                                                dtype_code(w), stream_ptr(x.device)), "mta_head_linear_softmax_fwd")
+    return y
+
+
 def softmax_fwd(x: torch.Tensor, causal: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 row softmax over keys q <= p; zeros above the diagonal.  x (N,C,P,Q)."""
     x = _cuda_contig(x, "input")

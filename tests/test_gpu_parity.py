@@ -166,6 +166,44 @@ def test_softmax(S, dtype):
     one_stage_close(npf(y2), ref, dtype, f"softmax of -inf filled S={S}")
 
 
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("C,S", [(16, 72), (16, 520), (7, 64), (32, 136), (4, 8), (16, 1304), (48, 40), (16, 67)])
+def test_head_linear_softmax(C, S, dtype, variant):
+    """Head mix + softmax in one pass (variant 0 where the shape allows it) against the oracle's two stages."""
+    g = torch.Generator().manual_seed(900 + C + S)
+    x = (3 * torch.randn(2, C, S, S, generator=g)).to(dtype)          # conv-output-like logits, peaked softmax
+    W32 = torch.eye(C) + 0.5 * torch.randn(C, C, generator=g)          # not representable in 16 bits
+    W = W32 if variant == 0 else W32.to(dtype)
+    _lib.set_variant("fused", variant)
+    try:
+        y = ops.head_linear_softmax_fwd(x.to(DEV), W.to(DEV))
+    finally:
+        _lib.set_variant("fused", 0)
+    _lib.device_status()
+    mixed = orc.head_linear(npf(x), npf(W), True, float("-inf"), ROUND[dtype])
+    ref = orc.softmax(mixed, True, ROUND[dtype])
+    # a logit that rounds the other way (fp32 against the oracle's double accumulation) moves its probability by up to
+    # one ulp of the LOGIT, relative
+    tol = 2.0 * ULP[dtype] * max(1.0, float(np.max(np.abs(mixed[np.isfinite(mixed)]))))
+    assert max_abs(npf(y), ref) <= tol, f"head mix + softmax C={C} S={S}: {max_abs(npf(y), ref):.3e} > {tol:.3e}"
+    iu = np.triu_indices(S, 1)
+    assert np.all(npf(y)[..., iu[0], iu[1]] == 0)
+    np.testing.assert_allclose(npf(y).sum(-1), 1.0, atol=4 * ULP[dtype] * np.sqrt(S) + 1e-6)
+
+
+def test_head_linear_softmax_is_reproducible_and_ignores_upper_input():
+    inp = make_head_linear_inputs(1, 16, 264, torch.bfloat16, seed=41)
+    x = (inp["x"].float() * 40).to(torch.bfloat16).to(DEV)
+    y = ops.head_linear_softmax_fwd(x, inp["W"].to(DEV))
+    xn = x.clone()
+    iu = torch.triu_indices(264, 264, 1)
+    xn[..., iu[0], iu[1]] = float("nan")
+    assert torch.equal(ops.head_linear_softmax_fwd(xn, inp["W"].to(DEV)), y)
+    two = ops.softmax_fwd(ops.head_linear_fwd(x, inp["W"].to(DEV), True, float("-inf")), True)
+    assert rel_max(npf(y), npf(two)) <= 2 * ULP[torch.bfloat16]
+
+
 @pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("S,D", [(5, 8), (65, 16), (130, 64), (256, 128), (128, 64), (200, 128), (8, 64), (1000, 128)])
