@@ -7,8 +7,9 @@ over one synthetic batch of the workload (default c4: B8 H16 S4096 D128 bf16, ca
 mixes 16x16, post-softmax conv 3x3).  Rank 0 prints ONE JSON line.
 
   value     tokens/s of the whole job with inputs resident in HBM (CUDA events, max over ranks)
-  e2e       tokens/s through the module's forward with HOST buffers: pinned host -> device copies of
-            q,k,v and the device -> host copy of the output are inside the timed region
+  e2e       tokens/s through the module's forward_host with HOST buffers: pinned host -> device copies of
+            q,k,v and the device -> host copy of the output are inside the timed region (the library
+            overlaps them with the computation, batch chunk by batch chunk)
   roofline  the dominant kernel of the step, timed alone with CUDA events, against the measured peak
   cpu_baseline  the CPU port of the reference's algorithm (oracle/, C + OpenMP) on a bounded sample of
             the same workload, on this box's host cores (rank 0, N=1 only)
@@ -173,39 +174,38 @@ def event_time_ms(fn, iters: int) -> float:
     return s.elapsed_time(e) / iters
 
 
-def stage_breakdown(wl: MTAWorkload, d, peaks):
-    """Times every kernel of the step alone (CUDA events on the launching stream, 3 warm-up + 5 timed launches;
-    each launch streams gigabytes, far more than L2) and returns the list plus the roofline entry of the slowest.
-    Algorithmic traffic of a score-plane stage as the stand-alone entry points run it: read the lower triangle
-    once and write the whole output plane (the zero / fill above the diagonal is part of what the call returns)."""
-    from multitokenatention_triton_b200 import ops
-    es = d["q"].element_size()
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per lower-triangle score element of one launch, from ncu
+# captures of smaller cases of the same kernels (the summaries under profiles/ give the commands); a launch's traffic
+# grows in proportion to the triangle it processes.
+NCU_DRAM_BYTES_PER_LOWER_ELEMENT = {}
+
+
+def stage_table(wl: MTAWorkload, samples, peaks):
+    """Per-stage device times of the forward as it runs in the step (CUDA events the library records on the launching
+    stream between its kernels: `samples` = list of [(stage, ms)] per traced step) -> one row per kernel with its
+    roofline.  Algorithmic work of a launch: a score-plane stage reads the lower triangle of its input planes once and
+    writes the lower triangle of its output planes once (nothing above the diagonal is touched inside the forward);
+    the two contractions are counted by their flops and by the triangle they write / read."""
+    es = torch.empty(0, dtype=wl.dtype).element_size()
     lower = wl.lower_elements()
-    plane_bytes = float(es) * (lower + wl.B * wl.H * wl.S * wl.S)      # read lower + write full
-    scale = wl.D ** -0.5
-    s = ops.qk_scores_fwd(d["q"], d["k"], scale, True)
-    c1 = ops.conv2d_fwd(s, d["w1"], True)
-    stages = [
-        ("qk_scores", lambda: ops.qk_scores_fwd(d["q"], d["k"], scale, True, out=s), "tensor", 2.0 * wl.D * lower),
-        ("conv1", lambda: ops.conv2d_fwd(s, d["w1"], True), "hbm", plane_bytes),
-        ("head_mix1", lambda: ops.head_linear_fwd(c1, d["W1"], True, 0.0), "hbm", plane_bytes),
-        ("softmax", lambda: ops.softmax_fwd(c1, True), "hbm", plane_bytes),
-        ("conv2", lambda: ops.conv2d_fwd(s, d["w2"], True), "hbm", plane_bytes),
-        ("pv", lambda: ops.pv_fwd(c1, d["v"], True), "tensor", 2.0 * wl.D * lower),
-    ]
+    qkv_bytes = float(es) * wl.B * wl.H * wl.S * wl.D
+    acc = {}
+    for step in samples:
+        for name, ms in step:
+            acc.setdefault(name, []).append(ms)
     out = []
-    for name, fn, bound, work in stages:
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        ms = event_time_ms(fn, 5)
-        if bound == "hbm":
-            ach, peak, unit = work / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+    for name, vals in acc.items():
+        ms = sum(vals) / len(vals)
+        row = {"kernel": name, "ms": ms, "samples": len(vals)}
+        if name in ("qk_scores", "pv"):
+            nbytes = float(es) * lower + 2 * qkv_bytes        # the score triangle written (read) + two operands
+            row.update(bound="hbm", tflops=2.0 * wl.D * lower / (ms * 1e-3) / 1e12)
         else:
-            ach, peak, unit = work / (ms * 1e-3) / 1e12, peaks["bf16_tflops"], "TFLOP/s"
-        out.append({"kernel": name, "ms": ms, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak})
-    del s, c1
-    torch.cuda.empty_cache()
+            nbytes = 2.0 * es * lower
+            row.update(bound="hbm")
+        ach = nbytes / (ms * 1e-3) / 1e9
+        row.update(bytes_algorithmic=nbytes, achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
+        out.append(row)
     return out
 
 
@@ -282,12 +282,18 @@ def main():
         sampler.start()
     barrier()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    _lib.set_stage_trace(True)                     # the library brackets its kernels with events on this stream
     s.record()
     for _ in range(args.steps):
         step()
     e.record()
     barrier()
     launches = _lib.launch_count()
+    stage_samples = [_lib.stage_times_ms()]        # the last step of the timed region ...
+    for _ in range(4):                             # ... and four more steps, read one by one
+        step()
+        stage_samples.append(_lib.stage_times_ms())
+    _lib.set_stage_trace(False)
     ms_total = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
     clocks = sampler.stop() if rank == 0 else None
     if dist is not None:
@@ -300,44 +306,38 @@ def main():
     e2e = None
     if not args.no_extras:
         out_host = torch.empty((wl.B, wl.H, wl.S, wl.D), dtype=wl.dtype).pin_memory()
-        dq, dk, dv = (torch.empty_like(d[k]) for k in ("q", "k", "v"))
 
         def e2e_step():
-            dq.copy_(host["q"], non_blocking=True)
-            dk.copy_(host["k"], non_blocking=True)
-            dv.copy_(host["v"], non_blocking=True)
-            with torch.no_grad():
-                o = model(dq, dk, dv, None, None)            # (B,S,H,D) view of a (B,H,S,D) tensor
-            out_host.copy_(o.transpose(1, 2), non_blocking=True)
+            with torch.no_grad():                            # blocks until out_host is complete
+                model.forward_host(host["q"], host["k"], host["v"], out=out_host)
 
         for _ in range(2):
             e2e_step()
         barrier()
         n_e2e = max(2, min(args.steps, 5))
-        s.record()
-        for _ in range(n_e2e):
+        t0 = time.perf_counter()                             # the call runs on the library's own streams and blocks:
+        for _ in range(n_e2e):                               # the host clock around it is the end-to-end time
             e2e_step()
-        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([(time.perf_counter() - t0) * 1e3], device=dev, dtype=torch.float64)
         barrier()
-        t = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         h2d = sum(host[k].numel() * host[k].element_size() for k in host)
         d2h = out_host.numel() * out_host.element_size()
         e2e = {"value": tokens / (float(t.item()) / n_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "steps": n_e2e}
-        del dq, dk, dv
+               "d2h_bytes_per_step": d2h, "steps": n_e2e,
+               "path": "MTAAttentionTriton.forward_host -> mta_fused_fwd_host: batch chunks on three streams, host clock around the blocking call"}
 
     # ---- per-kernel breakdown and roofline (rank 0) ----------------------------------------------
     roofline, stages, cpu = None, None, None
-    if rank == 0 and not args.no_extras:
-        try:
-            stages = stage_breakdown(wl, d, peaks)
-            top = max(stages, key=lambda r: r["ms"])
-            roofline = {"kernel": top["kernel"], "bound": top["bound"], "achieved": top["achieved"], "peak": top["peak"],
-                        "unit": top["unit"], "frac": top["frac"], "traffic": None, "peak_kind": peak_kind}
-        except Exception as ex:  # keep the headline even if the breakdown runs out of memory
-            stages = [{"error": f"{type(ex).__name__}: {ex}"}]
+    if rank == 0:
+        stages = stage_table(wl, stage_samples, peaks)
+        top = max(stages, key=lambda r: r["ms"])
+        per_lower = NCU_DRAM_BYTES_PER_LOWER_ELEMENT.get(top["kernel"])
+        roofline = {"kernel": top["kernel"], "bound": top["bound"], "achieved": top["achieved"], "peak": top["peak"],
+                    "unit": top["unit"], "frac": top["frac"],
+                    "traffic": per_lower * wl.lower_elements() if per_lower is not None else None, "peak_kind": peak_kind}
     if rank == 0 and world == 1 and not args.no_extras:
         v, cores, desc = cpu_port_tokens_per_s(wl, 15.0)
         cpu = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}

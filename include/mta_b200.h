@@ -130,6 +130,29 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
                   int w_dtype, void* stream);
 
 /*
+ * mta_fused_fwd (all query rows) for a caller whose q, k, v and o live in HOST memory (page-locked memory lets the
+ * copies overlap; pageable memory works but serialises them): the batch is cut into chunks of `chunk_batch` batch
+ * elements (0 = choose) and three internal CUDA streams overlap the host->device copy of chunk c+1, the forward
+ * of chunk c and the device->host copy of chunk c-1.  Stands in for .cuda() / MTAAttentionTriton.forward
+ * (mta_attention_triton.py:61-92) / .cpu() done back to back.  w1, W1, w2, W2 are DEVICE pointers on the current
+ * device.  Blocks until o is complete.  Staging and scratch memory are allocated on the first call per device,
+ * reused and grown by later calls, and freed by mta_host_pipeline_release() (current device).
+ */
+int mta_fused_fwd_host(const void* q, const void* k, const void* v, const void* w1, const void* W1, const void* w2,
+                       const void* W2, void* o, int B, int H, int S, int D, int cq, int ck, int cq2, int ck2,
+                       int causal, int dtype, int w_dtype, int chunk_batch);
+int mta_host_pipeline_release(void);
+
+/*
+ * Stage tracing of mta_fused_fwd (calling thread): after mta_set_stage_trace(1) every forward records a CUDA event
+ * on its stream before each stage and after the last.  mta_stage_times_ms waits for the latest forward and writes
+ * the device time of each of its stages (milliseconds) and, if `names` is not NULL, a static name per stage;
+ * returns the number of stages written (at most `capacity`), or -1 on a CUDA error.
+ */
+int mta_set_stage_trace(int on);
+int mta_stage_times_ms(float* ms, const char** names, int capacity);
+
+/*
  * Synchronises `stream` and reports whether any kernel launched on this device since the last call gave
  * up a bounded device-side wait (returns 4 and clears the flag) - kernels never spin without limit.
  */

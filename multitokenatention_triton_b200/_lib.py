@@ -39,6 +39,10 @@ SIGNATURES = {
     "mta_conv_attn_fwd_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_workspace_bytes": (_sz, [_i] * 11),
     "mta_fused_fwd": (_i, [_vp] * 9 + [_sz] + [_i] * 13 + [_vp]),
+    "mta_fused_fwd_host": (_i, [_vp] * 8 + [_i] * 12),
+    "mta_host_pipeline_release": (_i, []),
+    "mta_set_stage_trace": (_i, [_i]),
+    "mta_stage_times_ms": (_i, [_vp, _vp, _i]),
 }
 
 
@@ -98,3 +102,18 @@ def launch_count() -> int:
 
 def reset_launch_count() -> None:
     lib().mta_reset_launch_count()
+
+
+def set_stage_trace(on: bool) -> None:
+    """Switches the per-stage CUDA-event tracing of mta_fused_fwd on or off for the calling thread."""
+    check(lib().mta_set_stage_trace(int(bool(on))), "mta_set_stage_trace")
+
+
+def stage_times_ms():
+    """[(stage name, device milliseconds)] of the latest traced mta_fused_fwd (waits for it to finish)."""
+    ms = (ctypes.c_float * 8)()
+    names = (ctypes.c_char_p * 8)()
+    n = lib().mta_stage_times_ms(ms, names, 8)
+    if n < 0:
+        raise MTALibraryError("mta_stage_times_ms: CUDA error while reading the stage events")
+    return [(names[i].decode(), float(ms[i])) for i in range(n)]

@@ -37,12 +37,52 @@ Plan make_plan(int B, int H, int S, int cq, int cq2, int r0, int r1, int dtype) 
     return p;
 }
 
+// Stage tracing of mta_fused_fwd: when switched on, the forward records a CUDA event on its stream before every stage
+// and after the last, and mta_stage_times_ms turns the latest forward's events into per-stage device times.
+constexpr int MAX_STAGES = 8;
+thread_local bool g_trace_on = false;
+thread_local cudaEvent_t g_trace_ev[MAX_STAGES + 1] = {};
+thread_local const char* g_trace_name[MAX_STAGES] = {};
+thread_local int g_trace_n = 0;
+
+int trace_mark(const char* name, cudaStream_t st) {
+    if (!g_trace_on || g_trace_n >= MAX_STAGES) return MTA_OK;
+    if (!g_trace_ev[g_trace_n]) MTA_CUDA_OK(cudaEventCreate(&g_trace_ev[g_trace_n]));
+    MTA_CUDA_OK(cudaEventRecord(g_trace_ev[g_trace_n], st));
+    g_trace_name[g_trace_n++] = name;
+    return MTA_OK;
+}
+int trace_end(cudaStream_t st) {
+    if (!g_trace_on) return MTA_OK;
+    if (!g_trace_ev[g_trace_n]) MTA_CUDA_OK(cudaEventCreate(&g_trace_ev[g_trace_n]));
+    MTA_CUDA_OK(cudaEventRecord(g_trace_ev[g_trace_n], st));
+    return MTA_OK;
+}
+
 }  // namespace
 }  // namespace mta
 
 using namespace mta;
 
 extern "C" {
+
+int mta_set_stage_trace(int on) {
+    g_trace_on = on != 0;
+    g_trace_n = 0;
+    return MTA_OK;
+}
+
+int mta_stage_times_ms(float* ms, const char** names, int capacity) {
+    if (!ms || capacity < 0) return -1;
+    const int n = g_trace_n < capacity ? g_trace_n : capacity;
+    if (g_trace_n == 0) return 0;
+    if (cudaEventSynchronize(g_trace_ev[g_trace_n]) != cudaSuccess) return -1;
+    for (int i = 0; i < n; ++i) {
+        if (cudaEventElapsedTime(&ms[i], g_trace_ev[i], g_trace_ev[i + 1]) != cudaSuccess) return -1;
+        if (names) names[i] = g_trace_name[i];
+    }
+    return n;
+}
 
 size_t mta_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int cq2, int ck2, int q_row_begin,
                            int q_row_end, int dtype) {
@@ -84,6 +124,8 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     const float scale = 1.0f / sqrtf((float)D);
     const int round16 = dtype != MTA_F32;
     int rc;
+    g_trace_n = 0;
+    if ((rc = trace_mark("qk_scores", st))) return rc;
     if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, scale, round16, causal, pl.ra, pl.r1, dtype, st))) return rc;
     // mta_set_variant("fused", 2): two fused "conv + head mix" launches with the softmax folded into them.  Measured at
     // B8 H16 S4096: 12.1 ms per forward against 7.8 ms for the stage-by-stage pipeline below - both the conv and the
@@ -92,27 +134,39 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     if (variant("fused") == 2 && conv_mix_supported(H, S, cq, ck, causal, dtype, w_dtype, bufA, bufB) &&
         conv_mix_supported(H, S, cq2, ck2, causal, dtype, w_dtype, bufA, bufB)) {
         const long nrows = pl.r1 - pl.ra;
+        if ((rc = trace_mark("conv1+head_mix1", st))) return rc;
         if ((rc = conv_mix_prepare(w1, w_dtype, H, cq, ck, dtype, table1, st))) return rc;
         if ((rc = conv_mix_prepare(w2, w_dtype, H, cq2, ck2, dtype, table2, st))) return rc;
         if ((rc = conv_mix_launch(bufA, pv, nrows, table1, W1, w_dtype, bufB, pv, B, H, S, cq, ck, pl.rb, pl.r1, nullptr, stats,
                                   pl.rb, pl.r1 - pl.rb, dtype, st)))
             return rc;
+        if ((rc = trace_mark("softmax+conv2+head_mix2", st))) return rc;
         if ((rc = conv_mix_launch(bufB, pv, nrows, table2, W2, w_dtype, bufA, pv, B, H, S, cq2, ck2, pl.r0, pl.r1, stats, nullptr,
                                   pl.rb, pl.r1 - pl.rb, dtype, st)))
             return rc;
-        return pv_launch(bufA, pv, nrows, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st);
+        if ((rc = trace_mark("pv", st))) return rc;
+        if ((rc = pv_launch(bufA, pv, nrows, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st))) return rc;
+        return trace_end(st);
     }
+    if ((rc = trace_mark("conv1", st))) return rc;
     if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
     // the first head mix and the softmax run as one kernel where it applies (mta_set_variant("fused", 1) keeps them apart)
     if (variant("fused") != 1 && head_mix_softmax_supported(bufB, pv, bufA, pv, H, S, causal, dtype)) {
+        if ((rc = trace_mark("head_mix1+softmax", st))) return rc;
         if ((rc = head_mix_softmax_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, pl.rb, pl.r1, false, dtype, st))) return rc;
     } else {
+        if ((rc = trace_mark("head_mix1", st))) return rc;
         if ((rc = head_linear_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.rb, pl.r1, false, dtype, st))) return rc;
+        if ((rc = trace_mark("softmax", st))) return rc;
         if ((rc = softmax_launch(bufA, pv, bufA, pv, planes, S, S, causal, pl.rb, pl.r1, false, 1.0f, dtype, st))) return rc;
     }
+    if ((rc = trace_mark("conv2", st))) return rc;
     if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w2, w_dtype, bufB, pv, planes, H, S, S, cq2, ck2, causal, pl.r0, pl.r1, !causal, dtype, st))) return rc;
+    if ((rc = trace_mark("head_mix2", st))) return rc;
     if ((rc = head_linear_launch(bufB, pv, W2, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.r0, pl.r1, false, dtype, st))) return rc;
-    return pv_launch(bufA, pv, pl.r1 - pl.ra, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st);
+    if ((rc = trace_mark("pv", st))) return rc;
+    if ((rc = pv_launch(bufA, pv, pl.r1 - pl.ra, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st))) return rc;
+    return trace_end(st);
 }
 
 size_t mta_conv_attn_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int dtype) {

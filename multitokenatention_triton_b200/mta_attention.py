@@ -68,6 +68,16 @@ class MTAAttentionTriton(nn.Module):
         output = ops.pv_fwd(scores, xv, causal=True)
         return output.transpose(1, 2)
 
+    def forward_host(self, xq, xk, xv, out=None, chunk_batch: int = 0):
+        """forward for HOST tensors (B,H,S,D), ideally page-locked: the library overlaps the transfers with the
+        computation chunk by chunk, and the result comes back as a host tensor, (B,S,H,D) view as forward returns."""
+        if not self.causal:
+            raise NotImplementedError("MTAAttentionTriton without a mask requires causal=True, as in the reference's benchmarks")
+        o = ops.mta_fused_fwd_host(xq, xk, xv, self.mta_conv_triton.weight, self.wpsm_triton.weight,
+                                   self.mta_conv_after_sm_triton.weight, self.wposm_triton.weight, causal=True, out=out,
+                                   chunk_batch=chunk_batch)
+        return o.transpose(1, 2)
+
     def reset_mta_parameters(self, init_std=None):
         """Initialise as the reference does (mta_attention_triton.py:129-145): conv kernels by
         `mta.init_method`, both head mixes to the identity."""

@@ -168,3 +168,38 @@ def mta_fused_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w1: torch.T
                               cq2, ck2, r0, r1, int(bool(causal)), dtype_code(q), dtype_code(w1), stream_ptr(q.device)),
               "mta_fused_fwd")
     return out
+
+
+def mta_fused_fwd_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w1: torch.Tensor, W1: torch.Tensor,
+                       w2: torch.Tensor, W2: torch.Tensor, causal: bool = True, out: Optional[torch.Tensor] = None,
+                       chunk_batch: int = 0) -> torch.Tensor:
+    """Full MTA forward for HOST tensors q, k, v (B,H,S,D), ideally page-locked: copies in, computes and copies out
+    chunk by chunk on three streams inside the library, and returns a page-locked host tensor (B,H,S,D) once it is
+    complete.  The weights are the module's device tensors; their device is the one that computes."""
+    for name, t in (("xq", q), ("xk", k), ("xv", v)):
+        if t.is_cuda or not t.is_contiguous():
+            raise MTALibraryError(f"{name} must be a contiguous host tensor, got device={t.device} contiguous={t.is_contiguous()}")
+    B, H, S, D = q.shape
+    assert k.shape == q.shape and v.shape == q.shape and k.dtype == q.dtype and v.dtype == q.dtype
+    w1, w2 = _weight(w1, q, "conv weight"), _weight(w2, q, "post-softmax conv weight")
+    W1, W2 = _weight(W1, q, "head-mix weight"), _weight(W2, q, "post-softmax head-mix weight")
+    if len({w1.dtype, w2.dtype, W1.dtype, W2.dtype}) != 1:
+        w1, w2, W1, W2 = (t.float() for t in (w1, w2, W1, W2))
+    _, cq, ck = w1.shape
+    _, cq2, ck2 = w2.shape
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+    elif out.is_cuda or not out.is_contiguous() or out.shape != q.shape or out.dtype != q.dtype:
+        raise MTALibraryError("out must be a contiguous host tensor with the shape and dtype of xq")
+    with torch.cuda.device(w1.device):
+        torch.cuda.current_stream().synchronize()            # weights written on torch's stream are read on the library's
+        check(lib().mta_fused_fwd_host(q.data_ptr(), k.data_ptr(), v.data_ptr(), w1.data_ptr(), W1.data_ptr(), w2.data_ptr(),
+                                       W2.data_ptr(), out.data_ptr(), B, H, S, D, cq, ck, cq2, ck2, int(bool(causal)),
+                                       dtype_code(q), dtype_code(w1), int(chunk_batch)), "mta_fused_fwd_host")
+    return out
+
+
+def host_pipeline_release(device: Optional[torch.device] = None) -> None:
+    """Frees the staging and scratch memory mta_fused_fwd_host keeps on `device` (default: the current one)."""
+    with torch.cuda.device(device):
+        check(lib().mta_host_pipeline_release(), "mta_host_pipeline_release")

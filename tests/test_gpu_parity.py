@@ -5,6 +5,8 @@ Tolerances are those of the parity contract (tests/util.py): float32 max abs err
 dtypes <= 2e-2 relative, norm-wise.  Stand-alone ops are held to a much tighter bound because a single
 stage only differs from the oracle by summation order and one rounding.
 """
+import dataclasses
+
 import numpy as np
 import pytest
 import torch
@@ -302,6 +304,45 @@ def test_mta_forward_fused_stages_agree_with_stage_by_stage(name):
     assert torch.equal(part[:, :, 33:97], fused[:, :, 33:97])
     a = [npf(inp[k]) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
     assert_parity(npf(fused), orc.mta_fwd(*a, True, orc.ROUND_NONE), wl.dtype, f"{name} fused stages vs oracle")
+
+
+def test_stage_trace_reports_every_kernel_of_the_forward():
+    wl = MTA_CASES["s128_11x15_bf16"]
+    inp = make_mta_inputs(wl)
+    args = [inp[k].to(DEV) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    _lib.set_stage_trace(True)
+    try:
+        ops.mta_fused_fwd(*args, True)
+        got = _lib.stage_times_ms()
+        assert [n for n, _ in got] == ["qk_scores", "conv1", "head_mix1+softmax", "conv2", "head_mix2", "pv"]
+        assert all(0.0 < ms < 100.0 for _, ms in got)
+        _lib.set_variant("fused", 1)
+        ops.mta_fused_fwd(*args, True)
+        assert [n for n, _ in _lib.stage_times_ms()] == ["qk_scores", "conv1", "head_mix1", "softmax", "conv2", "head_mix2", "pv"]
+    finally:
+        _lib.set_variant("fused", 0)
+        _lib.set_stage_trace(False)
+    ops.mta_fused_fwd(*args, True)
+    assert _lib.stage_times_ms() == []
+
+
+@pytest.mark.parametrize("chunk", [0, 1, 2, 3])
+@pytest.mark.parametrize("name", ["c1", "s128_11x15_bf16"])
+def test_mta_forward_host_matches_device_forward(name, chunk):
+    """Host tensors in, host tensor out, batch chunks overlapped on three streams: same bits as the device forward."""
+    wl = dataclasses.replace(MTA_CASES[name], B=5)
+    inp = make_mta_inputs(wl)
+    m = build_mta(wl, inp, True)
+    with torch.no_grad():
+        want = m(inp["q"].to(DEV), inp["k"].to(DEV), inp["v"].to(DEV), None, None)
+        host = [inp[k].pin_memory() for k in ("q", "k", "v")]
+        got = m.forward_host(*host, chunk_batch=chunk)
+        assert not got.is_cuda and got.shape == want.shape
+        assert torch.equal(got, want.cpu())
+        again = m.forward_host(inp["q"], inp["k"], inp["v"], chunk_batch=chunk)      # pageable memory works too
+        assert torch.equal(again, got)
+    _lib.device_status()
+    ops.host_pipeline_release()
 
 
 @pytest.mark.parametrize("name,rows", [("ragged_f32", (3, 20)), ("ragged_f32", (64, 65)), ("s130_6x11_bf16", (17, 130)),
