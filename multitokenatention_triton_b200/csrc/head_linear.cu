@@ -88,6 +88,22 @@ __device__ __forceinline__ void st_global_v8(void* p, const uint4& a, const uint
                  "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
                  : "memory");
 }
+// The same store with an L2 eviction policy (createpolicy) attached.
+__device__ __forceinline__ void st_global_v8_hint(void* p, const uint4& a, const uint4& b, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8}, %9;" ::"l"(p), "r"(a.x), "r"(a.y),
+                 "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 __device__ __forceinline__ void ld_global_v8(const void* p, uint4& a, uint4& b) {
     asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
@@ -257,10 +273,11 @@ __device__ __forceinline__ void stat_merge(float& m, float& s, float m2, float s
 
 constexpr int MS_DEPTH = 4;        // ring slots per warp: loads run three 64-key blocks ahead
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid, uint64_t policy) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
     const int n = valid ? 16 : 0;                  // 0 source bytes: the 16 destination bytes are zero filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(d), "l"(gsrc), "r"(n), "l"(policy)
+                 : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -295,8 +312,14 @@ __device__ __forceinline__ void mma_tf32_m16n8k8_first(float (&d)[4], const uint
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
+#ifndef MTA_MS_WARPS
+#define MTA_MS_WARPS 4             // warps of the CTA that owns a row
+#endif
+#ifndef MTA_MS_MIN_CTAS
+#define MTA_MS_MIN_CTAS 4          // resident CTAs per SM the register allocation aims at
+#endif
 template <typename T, int CP, bool SPLITW, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 4)
+__global__ void __launch_bounds__(WARPS * 32, MTA_MS_MIN_CTAS)
 head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype, T* y,
                         PlaneView yv, int C, int Q, int row_end, int write_upper) {
     constexpr int KSTEPS = CP / 8;
@@ -314,6 +337,9 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
     const bool wide = rows_aligned32(y, yv);
     // key blocks wholly below the diagonal take the short path when every MMA row and column is a real head
     const bool fast = wide && C == CP && C == 16 * MT;
+    // L2 policies: the inputs and the final probabilities stream through (evict first); the logits written in phase 1
+    // are read back in phase 2 and should stay (evict last) - a quarter of them did not without the hints (measured)
+    const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
 
     uint32_t wa[MT][KSTEPS][4];
     uint32_t wl[SPLITW ? MT : 1][SPLITW ? KSTEPS : 1][4];
@@ -358,7 +384,7 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
 #pragma unroll
         for (int j = 0; j < NLOAD; ++j) {
             const bool ok = in_ok && t + 4 * j < C;
-            cp_async16(ring + (slot * NLOAD + j) * 32, ok ? xin[j] + blk * KB : x, ok);       // zero fill when not ok
+            cp_async16(ring + (slot * NLOAD + j) * 32, ok ? xin[j] + blk * KB : x, ok, pol_stream);   // zero fill when not ok
         }
         cp_async_commit();
     };
@@ -429,7 +455,7 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
                     }
                     rs[mt][hh] = fmaf(rs[mt][hh], ex2f((rm[mt][hh] - m_new) * LOG2E), s0 + s1);
                     rm[mt][hh] = m_new;
-                    st_global_v8(yout[mt][hh] + key0, pk[0], pk[1]);
+                    st_global_v8_hint(yout[mt][hh] + key0, pk[0], pk[1], pol_keep);
                     continue;
                 }
                 // block on the diagonal (or a shape the short path does not take): keys past the diagonal are masked
@@ -505,18 +531,27 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
             (&r.x)[i] = pack2<T>(ex2f(fmaf(lo, LOG2E, -sh)), ex2f(fmaf(hi, LOG2E, -sh)));
         }
     };
+    // iterations whose two blocks lie wholly below the diagonal; their loads are issued one iteration ahead
+    auto whole = [&](int blk) { return fast && blk < nblk && (blk + WARPS + 1) * KB <= n_keys; };
+    auto load_pair = [&](int blk, uint4 (&r)[2][MT][2][2]) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    ld_global_v8(yout[mt][hh] + (blk + u * WARPS) * KB, r[u][mt][hh][0], r[u][mt][hh][1]);
+    };
+    uint4 raw[2][MT][2][2];
+    bool cur_whole = whole(warp);
+    if (cur_whole) load_pair(warp, raw);
 #pragma unroll 1
     for (int blk = warp; blk < nblk; blk += 2 * WARPS) {
         const int key0 = blk * KB;
-        uint4 raw[2][MT][2][2];
-        if (fast && key0 + (WARPS + 1) * KB <= n_keys) {   // both blocks wholly below the diagonal
-#pragma unroll
-            for (int u = 0; u < 2; ++u)
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
-                        ld_global_v8(yout[mt][hh] + key0 + u * WARPS * KB, raw[u][mt][hh][0], raw[u][mt][hh][1]);
+        if (cur_whole) {
+            uint4 nxt[2][MT][2][2];
+            const bool nxt_whole = whole(blk + 2 * WARPS);
+            if (nxt_whole) load_pair(blk + 2 * WARPS, nxt);
 #pragma unroll
             for (int u = 0; u < 2; ++u)
 #pragma unroll
@@ -525,8 +560,18 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
                     for (int hh = 0; hh < 2; ++hh) {
                         to_prob(raw[u][mt][hh][0], shift[mt][hh]);
                         to_prob(raw[u][mt][hh][1], shift[mt][hh]);
-                        st_global_v8(yout[mt][hh] + key0 + u * WARPS * KB, raw[u][mt][hh][0], raw[u][mt][hh][1]);
+                        st_global_v8_hint(yout[mt][hh] + key0 + u * WARPS * KB, raw[u][mt][hh][0], raw[u][mt][hh][1], pol_stream);
                     }
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        raw[u][mt][hh][0] = nxt[u][mt][hh][0];
+                        raw[u][mt][hh][1] = nxt[u][mt][hh][1];
+                    }
+            cur_whole = nxt_whole;
             continue;
         }
 #pragma unroll
@@ -558,6 +603,8 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
                         }
                     }
                 }
+        cur_whole = whole(blk + 2 * WARPS);
+        if (cur_whole) load_pair(blk + 2 * WARPS, raw);
     }
     if (write_upper) {                                     // probabilities above the diagonal are exactly 0
         const int v0 = (n_keys + 7) >> 3, nv = Q >> 3;
@@ -572,7 +619,7 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
 template <typename T, int CP>
 int launch_mix_softmax(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
                        int row_begin, int row_end, bool write_upper, cudaStream_t st) {
-    constexpr int WARPS = 4;
+    constexpr int WARPS = MTA_MS_WARPS;
     dim3 grid((unsigned)(row_end - row_begin), (unsigned)N);
     const size_t smem = (size_t)WARPS * MS_DEPTH * (CP / 4) * 32 * sizeof(uint4);
     if (smem > 48 * 1024) {
