@@ -59,6 +59,14 @@ __device__ __forceinline__ void mma_tf32_m16n8k8(float (&d)[4], const uint32_t (
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// d = a * b (no accumulator input: saves zeroing the accumulators of every key block).
+__device__ __forceinline__ void mma_tf32_m16n8k8_first(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 // Element e (0..7) of a 16-byte vector of 16-bit values, as the fp32/TF32 bit pattern.
 template <typename T> __device__ __forceinline__ uint32_t elem_bits(const uint4& v, int e);
 template <> __device__ __forceinline__ uint32_t elem_bits<__nv_bfloat16>(const uint4& v, int e) {
@@ -159,48 +167,64 @@ head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __rest
     const uint32_t fill2 = pack2<T>(fill, fill);
     const int p_first = row_begin + blockIdx.y * rows_per_cta;
     const int p_last = min(p_first + rows_per_cta, row_end);
-
-    for (int p = p_first; p < p_last; ++p) {
-        if (causal && key0 > p) {            // the whole 64-key block is above the diagonal: fill only
-            if (write_upper) {
+    const bool wide = rows_aligned32(y, yv);
+    // rows whose whole 64-key block lies above the diagonal are only filled; they come first
+    const int p_mix = causal ? min(max(p_first, key0), p_last) : p_first;
+    if (write_upper)
+        for (int p = p_first; p < p_mix; ++p) {
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        const int o = 16 * mt + g + 8 * hh;
-                        const int kq = key0 + 16 * t;
-                        if (o < C && kq < Q) {
-                            uint4* dst = reinterpret_cast<uint4*>(y + yv.at(n * C + o, p, kq));
-                            const uint4 f = make_uint4(fill2, fill2, fill2, fill2);
-                            dst[0] = f;
-                            if (kq + 8 < Q) dst[1] = f;
-                        }
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int o = 16 * mt + g + 8 * hh;
+                    const int kq = key0 + 16 * t;
+                    if (o < C && kq < Q) {
+                        uint4* dst = reinterpret_cast<uint4*>(y + yv.at(n * C + o, p, kq));
+                        const uint4 f = make_uint4(fill2, fill2, fill2, fill2);
+                        dst[0] = f;
+                        if (kq + 8 < Q) dst[1] = f;
                     }
-            }
-            continue;
+                }
         }
-        // lane (g,t) reads keys [key0+8g, key0+8g+8) of heads t, t+4, ..., t+4(NLOAD-1)
-        uint4 xr[NLOAD];
-        const int kq_in = key0 + 8 * g;
+    if (p_mix >= p_last) return;
+
+    // lane (g,t) reads keys [key0+8g, key0+8g+8) of heads t, t+4, ..., t+4(NLOAD-1); the next row's loads are issued
+    // before this row's math
+    const int kq_in = key0 + 8 * g;
+    const T* xin[NLOAD];
+#pragma unroll
+    for (int j = 0; j < NLOAD; ++j) xin[j] = x + xv.at(n * C + min(t + 4 * j, C - 1), p_mix, kq_in);
+    auto load_row = [&](int p, uint4 (&xr)[NLOAD]) {
         const bool in_ok = kq_in < Q && !(causal && kq_in > p);
 #pragma unroll
         for (int j = 0; j < NLOAD; ++j) {
-            const int h = t + 4 * j;
-            if (in_ok && h < C) xr[j] = __ldg(reinterpret_cast<const uint4*>(x + xv.at(n * C + h, p, kq_in)));
+            if (in_ok && t + 4 * j < C) xr[j] = __ldg(reinterpret_cast<const uint4*>(xin[j] + (long)(p - p_mix) * xv.width));
             else xr[j] = make_uint4(0u, 0u, 0u, 0u);
         }
+    };
+    uint4 xr[NLOAD];
+    load_row(p_mix, xr);
+#pragma unroll 1
+    for (int p = p_mix; p < p_last; ++p) {
+        uint4 xn[NLOAD];
+        if (p + 1 < p_last) load_row(p + 1, xn);
         // One MMA column index (n = g) per key offset e: column g of MMA e is key key0 + 8g + e.
         float acc[8][MT][4];
 #pragma unroll
         for (int e = 0; e < 8; ++e)
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                acc[e][mt][0] = acc[e][mt][1] = acc[e][mt][2] = acc[e][mt][3] = 0.0f;
 #pragma unroll
                 for (int ks = 0; ks < KSTEPS; ++ks) {
                     const uint32_t b0 = elem_bits<T>(xr[2 * ks], e), b1 = elem_bits<T>(xr[2 * ks + 1], e);
-                    if (SPLITW) mma_tf32_m16n8k8(acc[e][mt], wl[SPLITW ? mt : 0][SPLITW ? ks : 0], b0, b1);
-                    mma_tf32_m16n8k8(acc[e][mt], wa[mt][ks], b0, b1);
+                    if (SPLITW) {
+                        if (ks == 0) mma_tf32_m16n8k8_first(acc[e][mt], wl[SPLITW ? mt : 0][SPLITW ? ks : 0], b0, b1);
+                        else mma_tf32_m16n8k8(acc[e][mt], wl[SPLITW ? mt : 0][SPLITW ? ks : 0], b0, b1);
+                        mma_tf32_m16n8k8(acc[e][mt], wa[mt][ks], b0, b1);
+                    } else {
+                        if (ks == 0) mma_tf32_m16n8k8_first(acc[e][mt], wa[mt][ks], b0, b1);
+                        else mma_tf32_m16n8k8(acc[e][mt], wa[mt][ks], b0, b1);
+                    }
                 }
             }
         // D fragment: c0 (row g, col 2t) c1 (g, 2t+1) c2 (g+8, 2t) c3 (g+8, 2t+1); column m of MMA e is key
@@ -212,9 +236,23 @@ head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __rest
             for (int hh = 0; hh < 2; ++hh) {
                 const int o = 16 * mt + g + 8 * hh;
                 if (o >= C) continue;
+                const int k16 = key0 + 16 * t;
+                if (wide && k16 + 16 <= Q && !(diag && k16 + 15 > p)) {      // 16 valid keys: one 32-byte store
+                    uint4 o0, o1;
+                    o0.x = pack2<T>(acc[0][mt][2 * hh], acc[1][mt][2 * hh]);
+                    o0.y = pack2<T>(acc[2][mt][2 * hh], acc[3][mt][2 * hh]);
+                    o0.z = pack2<T>(acc[4][mt][2 * hh], acc[5][mt][2 * hh]);
+                    o0.w = pack2<T>(acc[6][mt][2 * hh], acc[7][mt][2 * hh]);
+                    o1.x = pack2<T>(acc[0][mt][2 * hh + 1], acc[1][mt][2 * hh + 1]);
+                    o1.y = pack2<T>(acc[2][mt][2 * hh + 1], acc[3][mt][2 * hh + 1]);
+                    o1.z = pack2<T>(acc[4][mt][2 * hh + 1], acc[5][mt][2 * hh + 1]);
+                    o1.w = pack2<T>(acc[6][mt][2 * hh + 1], acc[7][mt][2 * hh + 1]);
+                    st_global_v8(y + yv.at(n * C + o, p, k16), o0, o1);
+                    continue;
+                }
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
-                    const int kq = key0 + 16 * t + 8 * cc;
+                    const int kq = k16 + 8 * cc;
                     if (kq >= Q) continue;
                     float v[8];
 #pragma unroll
@@ -240,6 +278,8 @@ head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __rest
                     *reinterpret_cast<uint4*>(dst) = out;
                 }
             }
+#pragma unroll
+        for (int j = 0; j < NLOAD; ++j) xr[j] = xn[j];
     }
 }
 
@@ -302,14 +342,6 @@ template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float& l
     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
     lo = f.x;
     hi = f.y;
-}
-
-// d = a * b (no accumulator input: saves zeroing the accumulators of every key block).
-__device__ __forceinline__ void mma_tf32_m16n8k8_first(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 #ifndef MTA_MS_WARPS
