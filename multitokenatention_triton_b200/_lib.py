@@ -11,7 +11,8 @@ from typing import Optional
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libmta_b200.so")
+# MTA_B200_LIB names another build of the same library (A/B runs of compile-time variants); default: the in-tree one.
+LIB_PATH = os.environ.get("MTA_B200_LIB") or os.path.join(_PKG, "libmta_b200.so")
 
 MTA_F32, MTA_BF16, MTA_F16 = 0, 1, 2
 DTYPE_CODE = {torch.float32: MTA_F32, torch.bfloat16: MTA_BF16, torch.float16: MTA_F16}

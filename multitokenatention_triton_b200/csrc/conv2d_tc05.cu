@@ -8,14 +8,15 @@
 //
 // Persistent, warp-specialised kernel: one CTA per SM walks a contiguous range of 128 x 128 output tiles
 // (only tiles that touch keys <= query when causal):
-//   warp 0      TMA producer (also stores the zero tiles above the diagonal when the whole output is wanted): two 64-column boxes (128-byte swizzle) and one 16-column box (32-byte swizzle) per tile
+//   warp 0      TMA producer: two 64-column boxes (128-byte swizzle) and one 16-column box (32-byte swizzle) per tile
 //               bring the (128 + R-1) x 144 halo tile straight into the swizzled K-major layouts the MMA reads (3-stage ring; out-of-range rows / columns arrive as
 //               zero = the conv's zero padding)
 //   warps 2-3, 14-15  zero the keys above the causal diagonal in the staged tile (diagonal tiles only); rebuild the
 //               Toeplitz slices when the head changes
-//   warps 1,8,9 issue the MMAs into TMEM accumulator n % 2; each issuer owns a fixed set of 16-column output blocks
-//               (3 + 3 + 2), so every output element is accumulated by one thread in program order and the result
-//               does not depend on how the issuers interleave (66 MMAs per tile for a 6 x 11 kernel)
+//   warps 1, 8  issue the MMAs into TMEM accumulator n % 2; each issuer owns half of the 16-column output blocks,
+//               so every output element is accumulated by one thread in program order and the result does not
+//               depend on how the issuers interleave (60 MMAs per tile for a 6 x 11 kernel)
+//   warp 9      stores the zero tiles above the diagonal when the whole output is wanted
 //   warps 4-7, 10-13  epilogue (64 columns each): TMEM -> registers -> 16-bit -> swizzled shared-memory tile (double
 //               buffered) -> TMA tiled store (a thread owns one output row, so direct global stores would touch 32
 //               different lines per instruction)
@@ -75,11 +76,14 @@ constexpr int NBOX = 2;            // 64-column TMA boxes per staged tile (128-b
                                    // (32-byte swizzle) holds the last k-step
 constexpr int NSTAGE = 3;
 constexpr int OUT_BYTES = 2 * TM * 128;   // output staging: two 64-column boxes of 128 rows x 128 bytes, 128-byte swizzle
-constexpr int NISS = 3;            // MMA-issuing threads (warps 1, 8, 9)
-constexpr int MAXB = 4;            // MMAs per (row tap, term) of one issuer: its blocks + 1
-// First 16-column output block of issuer k (blocks 0-2, 3-5, 6-7).
-__host__ __device__ constexpr int issuer_block0(int k) { return k == 0 ? 0 : k == 1 ? 3 : k == 2 ? 6 : NB; }
-constexpr int THREADS = 512;       // warps: 0 producer, 1/8/9 MMA issuers, 2-3 and 14-15 tile fix-up, 4-7 and 10-13 epilogue
+#ifndef MTA_CONV_NISS
+#define MTA_CONV_NISS 2
+#endif
+constexpr int NISS = MTA_CONV_NISS;   // MMA-issuing threads (warps 1, 8): 1 or 2
+constexpr int ZERO_WARP = 9;          // the warp that stores the zero tiles above the diagonal
+// First 16-column output block of issuer k (two issuers: blocks 0-3 and 4-7).
+__host__ __device__ constexpr int issuer_block0(int k) { return NISS == 1 ? (k == 0 ? 0 : NB) : (k == 0 ? 0 : k == 1 ? 4 : NB); }
+constexpr int THREADS = 512;       // warps: 0 producer, 1 and 8 MMA issuers, 9 zero tiles, 2-3 and 14-15 tile fix-up, 4-7 and 10-13 epilogue
 
 template <typename T> struct AbFmt;
 template <> struct AbFmt<__nv_bfloat16> { static constexpr int value = 1; };
@@ -143,6 +147,43 @@ struct TileIter {
     __device__ int n0() const { return tn * TN; }
 };
 
+// The MMAs of one tile that issuer ISSUER is responsible for.  It owns output blocks [b0, b1]; the k-steps that
+// reach them are b0 .. b1 + 1.  k-step s is an N = 32 MMA onto blocks s-1 and s, except at the two ends of the range,
+// where only one half of the Toeplitz slice is used (N = 16): rows 16..31 (+256 bytes) onto block b0 for s = b0, rows
+// 0..15 onto block b1 for s = b1 + 1.  Per (row tap i, term) the k-steps b0+1, b0+3, ... come first: they touch every
+// owned block exactly once, so in the first batch they carry accumulate = 0.
+template <typename T, int ISSUER>
+__device__ __forceinline__ void issue_tile(uint32_t xa_addr, uint32_t d0, int R, int split_w, int box_bytes, int tb_off) {
+    constexpr uint32_t idesc32 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 32);
+    constexpr uint32_t idesc16 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 16);
+    constexpr int b0 = issuer_block0(ISSUER), b1 = issuer_block0(ISSUER + 1) - 1;
+    const uint64_t da0 = smem_desc_sw128(xa_addr, 16, 1024);
+    const uint64_t da3 = smem_desc_sw32(xa_addr + (uint32_t)(NBOX * box_bytes), 256);   // the last k-step: 32-byte-row box
+    const uint64_t db0 = smem_desc_plain(xa_addr + (uint32_t)tb_off, 512, 128);        // k chunks 512 bytes apart, 8-row groups 128
+    const int parts = split_w ? 2 : 1;
+    int batch = 0;
+#pragma unroll 1
+    for (int i = 0; i < R; ++i)
+#pragma unroll 1
+        for (int part = 0; part < parts; ++part, ++batch) {
+            const uint64_t db = db0 + (uint64_t)((i * 1024 + part * R * 1024) >> 4);
+            const uint64_t da = da0 + (uint64_t)((i * 128) >> 4);      // a row tap is the start address advanced by i rows
+            const uint64_t dl = da3 + (uint64_t)((i * 32) >> 4);
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass)
+#pragma unroll
+                for (int s = b0 + 1 - pass; s <= b1 + 1; s += 2) {
+                    const bool upper = s == b0, lower = s == b1 + 1;
+                    // k-steps 0..7 live in the two 128-byte-row boxes (four per box), k-step 8 in the 32-byte-row box
+                    const uint64_t adesc = s < 8 ? da + (uint64_t)(((s / 4) * box_bytes + (s % 4) * 32) >> 4) : dl;
+                    const uint64_t bdesc = db + (upper ? 16u : 0u);
+                    const uint32_t dcol = upper ? 16u * (uint32_t)s : 16u * (uint32_t)(s - 1);
+                    const uint32_t acc = (batch > 0 || pass > 0) ? 1u : 0u;
+                    mma_f16_ss(d0 + dcol, adesc, bdesc, (upper || lower) ? idesc16 : idesc32, acc);
+                }
+        }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS, 1)
 conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mx3,
@@ -153,10 +194,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     __shared__ __align__(8) uint64_t full_bar[NSTAGE], ready_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    // MMA schedule of one tile per issuer: up to 32 batches (R <= 16 row taps, two terms for fp32 weights) of up to
-    // MAXB MMAs.  x = A offset | B offset << 16 (16-byte units from the stage base), y = accumulator column | flags << 8
-    // (bit 0: N = 16, bit 1: accumulate, bit 2: A in the 32-byte-row box).
-    __shared__ uint2 sched[NISS * 32 * MAXB];
+    __shared__ int tiles_loaded;               // compute tiles whose loads the producer has issued (paces the zero tiles)
     const int R = g.R, S = g.S;
     const int TH = TM + R - 1;
     const int box_bytes = (TH * 128 + 1023) & ~1023;          // one 64-column box, 1024-byte aligned (swizzle period)
@@ -178,6 +216,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     const long t_end = min(t_begin + per, g.total_tiles);
     const int my_tiles = t_end > t_begin ? (int)(t_end - t_begin) : 0;
 
+    if (tid == 0) tiles_loaded = 0;
     if (tid == 0) abort_flag = *reinterpret_cast<volatile int*>(err_flag);
     __syncthreads();
     if (abort_flag != 0 || my_tiles == 0) return;
@@ -199,32 +238,6 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         }
         __syncwarp();
         tmem_alloc(&tmem_slot, 2 * TN);
-    } else if ((warp == 1 || warp == 8 || warp == 9) && lane == 0) {
-        // This issuer's MMA schedule of one tile, in issue order.  It owns output blocks [b0, b1]; the k-steps that
-        // reach them are b0 .. b1 + 1.  k-step s is an N = 32 MMA onto blocks s-1 and s, except at the two ends of the
-        // range, where only one half of the Toeplitz slice is used (N = 16): rows 16..31 (+256 bytes) onto block b0 for
-        // s = b0, rows 0..15 onto block b1 for s = b1 + 1.  Batch = (row tap i, term); within a batch the k-steps
-        // b0+1, b0+3, ... come first (they touch every owned block exactly once: accumulate = 0 in the first batch).
-        const int issuer = warp == 1 ? 0 : warp - 7;
-        const int b0 = issuer_block0(issuer), b1 = issuer_block0(issuer + 1) - 1;
-        int batch = 0;
-        for (int i = 0; i < R; ++i)
-            for (int part = 0; part < (g.split_w ? 2 : 1); ++part, ++batch) {
-                int m = 0;
-                for (int pass = 0; pass < 2; ++pass)
-                    for (int s = b0 + 1 - pass; s <= b1 + 1; s += 2) {
-                        // k-steps 0..7 live in the two 128-byte-row boxes, k-step 8 in the 32-byte-row box
-                        const uint32_t a16 = s < 8 ? (uint32_t)(((s / 4) * box_bytes + i * 128 + (s % 4) * 32) >> 4)
-                                                   : (uint32_t)((NBOX * box_bytes + i * 32) >> 4);
-                        uint32_t b16 = (uint32_t)((tb_off + i * 1024 + part * R * 1024) >> 4);
-                        const bool upper = s == b0, lower = s == b1 + 1;
-                        if (upper) b16 += 16;
-                        const uint32_t dcol = upper ? 16u * (uint32_t)s : 16u * (uint32_t)(s - 1);
-                        const uint32_t acc = (batch > 0 || pass > 0) ? 1u : 0u;
-                        const uint32_t flags = ((upper || lower) ? 1u : 0u) | (acc << 1) | (s == 8 ? 4u : 0u);
-                        sched[(issuer * 32 + batch) * MAXB + m++] = make_uint2(a16 | (b16 << 16), dcol | (flags << 8));
-                    }
-            }
     }
     fence_before_sync();
     __syncthreads();
@@ -232,35 +245,11 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     const uint32_t tmem = tmem_slot;
 
     if (warp == 0) {
-        // ---------------- producer (and zero tiles) ----------------
-        // The tiles wholly above the diagonal are part of the output the API returns: they are written as TMA stores of
-        // a zero box, a share of them after every load, so they overlap the compute tiles' traffic.
-        const long active = (g.total_tiles + per - 1) / per;      // CTAs that own compute tiles (the others have returned)
-        const long zper = (g.zero_total + active - 1) / active;
-        const long z_begin = min((long)blockIdx.x * zper, g.zero_total), z_end = min(z_begin + zper, g.zero_total);
-        const long my_zero = z_end - z_begin;
-        if (my_zero > 0) {
-            for (int i = lane; i < TM * 128 / 16; i += 32) reinterpret_cast<uint4*>(zero_box)[i] = make_uint4(0u, 0u, 0u, 0u);
-            fence_proxy_async();
-        }
-        __syncwarp();
+        // ---------------- producer ----------------
         if (lane == 0) {
             PROF_DECL
             TileIter it;
             it.init(g, t_begin);
-            // zero-tile walker: (plane, row tile, column tile) with column tiles conv_key_tiles(tm) .. tiles_n - 1
-            int zp = 0, ztm = 0, ztn = 0;
-            if (my_zero > 0) {
-                zp = (int)(z_begin / g.zero_per_plane);
-                long r = z_begin - (long)zp * g.zero_per_plane;
-                for (ztm = 0;; ++ztm) {
-                    const int nz = g.tiles_n - conv_key_tiles(g, ztm);
-                    if (r < nz) break;
-                    r -= nz;
-                }
-                ztn = conv_key_tiles(g, ztm) + (int)r;
-            }
-            long zi = 0;
             for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
                 const int st = n % NSTAGE;
                 PROF_START
@@ -273,34 +262,59 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                     tma_load_3d(xa + j * box_bytes, &mx, &full_bar[st], it.n0() - pad8 + 64 * j, it.m0(g) - (R - 1) - g.x_row0,
                                 it.plane);
                 tma_load_3d(xa + NBOX * box_bytes, &mx3, &full_bar[st], it.n0() - pad8 + 128, it.m0(g) - (R - 1) - g.x_row0, it.plane);
-                const long z_target = my_zero * (n + 1) / my_tiles;
-                for (; zi < z_target; ++zi) {
-                    const int zm0 = g.row_begin + ztm * TM, zn0 = ztn * TN;
-                    tma_store_3d(&my, zero_box, zn0, zm0 - y_row0, zp);
-                    if (zn0 + 64 < g.W) tma_store_3d(&my, zero_box, zn0 + 64, zm0 - y_row0, zp);
-                    bulk_commit();
-                    if (++ztn == g.tiles_n) {
-                        do {
-                            if (++ztm == g.tiles_m) { ztm = 0; ++zp; }
-                        } while (conv_key_tiles(g, ztm) >= g.tiles_n && zi + 1 < my_zero);
-                        ztn = conv_key_tiles(g, ztm);
-                    }
+                *reinterpret_cast<volatile int*>(&tiles_loaded) = n + 1;
+            }
+            PROF_FLUSH(12, true)
+        }
+    } else if (warp == ZERO_WARP) {
+        // ---------------- zero tiles ----------------
+        // The tiles wholly above the diagonal are part of the output the API returns: this warp writes its share of
+        // them as TMA stores of a zero box, in step with the producer's progress through the compute tiles, so the two
+        // kinds of traffic overlap for the whole run instead of the zero stores flooding the memory system first.
+        const long active = (g.total_tiles + per - 1) / per;      // CTAs that own compute tiles (the others have returned)
+        const long zper = (g.zero_total + active - 1) / active;
+        const long z_begin = min((long)blockIdx.x * zper, g.zero_total), z_end = min(z_begin + zper, g.zero_total);
+        const long my_zero = z_end - z_begin;
+        if (my_zero > 0) {
+            for (int i = lane; i < TM * 128 / 16; i += 32) reinterpret_cast<uint4*>(zero_box)[i] = make_uint4(0u, 0u, 0u, 0u);
+            fence_proxy_async();
+        }
+        __syncwarp();
+        if (lane == 0 && my_zero > 0) {
+            // walker over (plane, row tile, column tile) with column tiles conv_key_tiles(tm) .. tiles_n - 1
+            int zp = (int)(z_begin / g.zero_per_plane), ztm = 0;
+            long r = z_begin - (long)zp * g.zero_per_plane;
+            for (;; ++ztm) {
+                const int nz = g.tiles_n - conv_key_tiles(g, ztm);
+                if (r < nz) break;
+                r -= nz;
+            }
+            int ztn = conv_key_tiles(g, ztm) + (int)r;
+            for (long zi = 0; zi < my_zero; ++zi) {
+                // zero tile zi is due once the producer has loaded compute tile zi * my_tiles / my_zero (bounded wait:
+                // the producer always reaches its last tile, and giving up early only changes the pacing)
+                const int due = (int)(zi * my_tiles / my_zero);
+                for (int spin = 0; *reinterpret_cast<volatile int*>(&tiles_loaded) < due && spin < (1 << 20); ++spin) __nanosleep(256);
+                const int zm0 = g.row_begin + ztm * TM, zn0 = ztn * TN;
+                tma_store_3d(&my, zero_box, zn0, zm0 - y_row0, zp);
+                if (zn0 + 64 < g.W) tma_store_3d(&my, zero_box, zn0 + 64, zm0 - y_row0, zp);
+                bulk_commit();
+                bulk_wait_read_1();
+                if (++ztn == g.tiles_n) {
+                    do {
+                        if (++ztm == g.tiles_m) { ztm = 0; ++zp; }
+                    } while (conv_key_tiles(g, ztm) >= g.tiles_n && zi + 1 < my_zero);
+                    ztn = conv_key_tiles(g, ztm);
                 }
             }
             bulk_wait_all();
-            PROF_FLUSH(12, true)
         }
-    } else if (warp == 1 || warp == 8 || warp == 9) {
+    } else if (warp == 1 || (warp == 8 && NISS >= 2)) {
         // ---------------- MMA issuers ----------------
-        // Issuing a tcgen05.mma whose descriptors differ from the previous one costs the issuing thread ~100 cycles
-        // here (measured), about twice the ~47 cycles the tensor core needs for it, so three threads issue, each onto
-        // its own output blocks: no ordering between the issuers is needed, and none affects the result.
-        constexpr uint32_t idesc32 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 32);
-        constexpr uint32_t idesc16 = instr_desc_f16(AbFmt<T>::value, 0, 0, TM, 16);
-        const int n_batch = R * (g.split_w ? 2 : 1);
-        const int issuer = warp == 1 ? 0 : warp - 7;          // 0, 1, 2
-        const int n_mma = issuer_block0(issuer + 1) - issuer_block0(issuer) + 1;     // MMAs per batch
-        const uint2* my_sched = sched + issuer * 32 * MAXB;
+        // Two threads issue, each onto its own output blocks, so no ordering between them is needed and none affects
+        // the result (measured at B8 H16 S4096, 6 x 11: one issuer 1.19 ms, two 0.94 ms, three 1.01 ms; the tensor pipe
+        // takes ~49 cycles per MMA, a single thread issues one per ~76).  The schedule of an issuer is compile-time (issue_tile<ISSUER>): every descriptor is the stage's
+        // base descriptor plus a constant and a multiple of the row tap, all warp-uniform values.
         PROF_DECL
         for (int n = 0; n < my_tiles; ++n) {
             const int st = n % NSTAGE, ab = n & 1;
@@ -312,23 +326,9 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             fence_after_sync();
             if (lane == 0) {
                 const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
-                const uint64_t da0 = smem_desc_sw128(xa_addr, 16, 1024);
-                const uint64_t da3 = smem_desc_sw32(xa_addr, 256);           // the last k-step reads the 32-byte-row box
-                const uint64_t db0 = smem_desc_plain(xa_addr, 512, 128);     // k chunks 512 bytes apart, 8-row groups 128
                 const uint32_t d0 = tmem + (uint32_t)(ab * TN);
-                // the table entries of a batch are fetched before its MMAs are issued
-                for (int b = 0; b < n_batch; ++b) {
-                    uint2 e[MAXB];
-#pragma unroll
-                    for (int j = 0; j < MAXB; ++j) e[j] = my_sched[b * MAXB + j];
-#pragma unroll
-                    for (int j = 0; j < MAXB; ++j)
-                        if (j < n_mma) {
-                            const uint32_t fl = e[j].y >> 8;
-                            mma_f16_ss(d0 + (e[j].y & 0xffu), ((fl & 4u) ? da3 : da0) + (e[j].x & 0xffffu), db0 + (e[j].x >> 16),
-                                       (fl & 1u) ? idesc16 : idesc32, (fl >> 1) & 1u);
-                        }
-                }
+                if (warp == 1) issue_tile<T, 0>(xa_addr, d0, R, g.split_w, box_bytes, tb_off);
+                else issue_tile<T, NISS >= 2 ? 1 : 0>(xa_addr, d0, R, g.split_w, box_bytes, tb_off);
                 mma_commit(&empty_bar[st]);
                 mma_commit(&acc_full[ab]);
             }
@@ -336,6 +336,8 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             PROF_ACC(3, true)
         }
         PROF_FLUSH(0, warp == 1)
+    } else if (warp == 8 || warp == 9) {
+        // issuer warp that this build does not use
     } else if (warp < 4 || warp >= 14) {
         // ---------------- (warps 2-3, 14-15) causal zeroing of the staged tile, Toeplitz slices ----------------
         const int ft = warp < 4 ? tid - 64 : tid - 448 + 64;     // 0..127
