@@ -177,7 +177,9 @@ def event_time_ms(fn, iters: int) -> float:
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per lower-triangle score element of one launch, from ncu
 # captures of smaller cases of the same kernels (the summaries under profiles/ give the commands); a launch's traffic
 # grows in proportion to the triangle it processes.
-NCU_DRAM_BYTES_PER_LOWER_ELEMENT = {}
+NCU_DRAM_BYTES_PER_LOWER_ELEMENT = {       # profiles/mta_forward_kernels_b1_s4096.md (B1 H16 S4096: 134.25 M scores)
+    "qk_scores": 2.01, "conv1": 4.07, "head_mix1+softmax": 3.63, "conv2": 4.00, "head_mix2": 3.73, "pv": 2.28,
+}
 
 
 def stage_table(wl: MTAWorkload, samples, peaks):
