@@ -131,10 +131,17 @@ def cpu_port_tokens_per_s(wl: MTAWorkload, budget_s: float, threads: int = 0):
     target = int(min(wl.S, max(16, n * budget_s / max(t, 1e-3)))) // 16 * 16 or n
     if target > n:
         t, n = run(target)
+    reps = 1
+    if n == wl.S and t < budget_s:             # a whole batch element is too short a sample: time several (same cost each)
+        reps = int(min(wl.B, max(1, budget_s // max(t, 1e-3))))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            run(n)
+        t = time.perf_counter() - t0
     desc = (f"CPU port (C, OpenMP) of the reference algorithm on batch element 0, query rows "
             f"[{max(0, mid - n // 2)},{max(0, mid - n // 2) + n}) of {wl.S} (block centred on S/2 = mean cost per token), "
-            f"all {wl.H} heads, {t:.1f} s")
-    return n / t, cores, desc
+            f"all {wl.H} heads, {reps} time(s), {t:.1f} s")
+    return reps * n / t, cores, desc
 
 
 def reference_arm(args, wl: MTAWorkload, rank: int):
