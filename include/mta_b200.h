@@ -112,6 +112,32 @@ int mta_conv_attn_fwd_static(const void* q, const void* k, const void* v, const 
                              int D, int cq, int ck, int causal, float scale, int dtype, int w_dtype, void* stream);
 
 /*
+ * Gradients of the two stand-alone ops (the reference's autograd backward of Conv2dTritonFunction,
+ * convolution_2d_trit.py:335-378, and of TritonLinearHeadFunction, triton_linear_head.py:321-370).
+ *
+ * mta_conv2d_bwd_input   dx[n,c,q,k] = sum_{i,j} w[c,i,j] * dyh[n,c,q-i+(R-1),k-j+(S-1)/2] for k <= q (everywhere if not
+ *                        causal), 0 above the diagonal; dyh = dy inside the plane and (causal) where key <= query, else 0
+ *                        (conv_bwd_input_kernel, :143-218).  dy, dx: (N,C,H,W) in `dtype`, the whole of dx is written.
+ * mta_conv2d_bwd_weight  dw[c,i,j] = sum_{n,q,k} xh[n,c,q+i-(R-1),k+j-(S-1)/2] * dyh[n,c,q,k] (conv_bwd_weight_kernel,
+ *                        :226-295).  dw: (C,R,S) float32 (the reference returns float64).  Partial sums go through the
+ *                        workspace and are added in a fixed order in double precision.
+ * mta_head_linear_bwd_input   dx[n,h,p,q] = sum_o Wm[o,h] * dy[n,o,p,q] for q <= p, 0 above the diagonal (the reference
+ *                        leaves those entries uninitialised; linear_head_kernel_backward_input, :142-207).
+ * mta_head_linear_bwd_weight  dW[o,h] = sum_{n,p,q<=p} dy[n,o,p,q] * x[n,h,p,q] (linear_head_kernel_backward_weight,
+ *                        :210-278).  dW: (C,C) float32; workspace as above.
+ */
+int mta_conv2d_bwd_input(const void* dy, const void* w, void* dx, int N, int C, int H, int W, int R, int S, int causal,
+                         int dtype, int w_dtype, void* stream);
+size_t mta_conv2d_bwd_weight_workspace_bytes(int N, int C, int H, int W, int R, int S);
+int mta_conv2d_bwd_weight(const void* x, const void* dy, float* dw, void* workspace, size_t workspace_bytes, int N, int C,
+                          int H, int W, int R, int S, int causal, int dtype, void* stream);
+int mta_head_linear_bwd_input(const void* dy, const void* Wm, void* dx, int N, int C, int P, int Q, int causal, int dtype,
+                              int w_dtype, void* stream);
+size_t mta_head_linear_bwd_weight_workspace_bytes(int C);
+int mta_head_linear_bwd_weight(const void* x, const void* dy, float* dW, void* workspace, size_t workspace_bytes, int N,
+                               int C, int P, int Q, int causal, int dtype, void* stream);
+
+/*
  * Full four-stage MTA forward: QK^T/sqrt(D) -> conv (w1) -> head mix (W1) -> softmax -> conv (w2) ->
  * head mix (W2) -> @V, for batch elements [0,B) and query rows [q_row_begin, q_row_end).
  * Replaces the body of MTAAttentionTriton.forward (mta_attention_triton.py:61-92) with use_mask=False;

@@ -32,6 +32,12 @@ SIGNATURES = {
     "mta_head_linear_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_softmax_fwd": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mta_head_linear_softmax_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "mta_conv2d_bwd_input": (_i, [_vp, _vp, _vp] + [_i] * 9 + [_vp]),
+    "mta_conv2d_bwd_weight_workspace_bytes": (_sz, [_i] * 6),
+    "mta_conv2d_bwd_weight": (_i, [_vp, _vp, _vp, _vp, _sz] + [_i] * 8 + [_vp]),
+    "mta_head_linear_bwd_input": (_i, [_vp, _vp, _vp] + [_i] * 7 + [_vp]),
+    "mta_head_linear_bwd_weight_workspace_bytes": (_sz, [_i]),
+    "mta_head_linear_bwd_weight": (_i, [_vp, _vp, _vp, _vp, _sz] + [_i] * 6 + [_vp]),
     "mta_qk_scores_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
     "mta_pv_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mta_conv_attn_workspace_bytes": (_sz, [_i] * 7),

@@ -1,8 +1,9 @@
 """Depthwise causal 2-D convolution over score planes: the module, with the reference's names.
 
 Mirrors Conv2dTritonFunction / Conv2dTriton of the reference (convolution_2d_trit.py:300-401): same
-constructor, same weight shape (C,R,S), same default initialisation, same forward semantics.  The
-forward runs the CUDA kernel behind mta_conv2d_fwd.
+constructor, same weight shape (C,R,S), same default initialisation, same forward and backward
+semantics.  The forward runs the CUDA kernel behind mta_conv2d_fwd, the backward those behind
+mta_conv2d_bwd_input / mta_conv2d_bwd_weight.
 """
 import torch
 import torch.nn as nn
@@ -14,11 +15,21 @@ from . import ops
 class Conv2dTritonFunction(Function):
     @staticmethod
     def forward(ctx, input, weight, causal):
+        ctx.save_for_backward(input, weight)
+        ctx.causal = causal
         return ops.conv2d_fwd(input, weight, causal)
 
     @staticmethod
     def backward(ctx, grad_output):
-        raise NotImplementedError("the B200 MTA library implements the forward pass only")
+        # the reference's backward (convolution_2d_trit.py:335-378); the weight gradient comes back in the weight's dtype
+        input, weight = ctx.saved_tensors
+        grad_input = grad_weight = None
+        grad_output = grad_output.to(input.dtype)
+        if ctx.needs_input_grad[0]:
+            grad_input = ops.conv2d_bwd_input(grad_output, weight, ctx.causal)
+        if ctx.needs_input_grad[1]:
+            grad_weight = ops.conv2d_bwd_weight(input, grad_output, tuple(weight.shape[1:]), ctx.causal).to(weight.dtype)
+        return grad_input, grad_weight, None
 
 
 class Conv2dTriton(nn.Module):

@@ -128,6 +128,83 @@ int mta_head_linear_softmax_fwd(const void* x, const void* Wm, void* y, int N, i
     return softmax_launch(y, v, y, v, (long)N * C, P, Q, 1, 0, P, true, 1.0f, x_dtype, st);
 }
 
+int mta_conv2d_bwd_input(const void* dy, const void* w, void* dx, int N, int C, int H, int W, int R, int S, int causal,
+                         int dtype, int w_dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "conv2d_bwd_input: unknown dtype code (dy %d, w %d)", dtype, w_dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && H >= 0 && W >= 0, "conv2d_bwd_input: bad shape N=%d C=%d H=%d W=%d", N, C, H, W);
+    MTA_REQUIRE(R >= 1 && S >= 1, "conv2d_bwd_input: kernel size %dx%d must be positive", R, S);
+    if ((long)N * H * W == 0) return MTA_OK;
+    MTA_REQUIRE(dy && w && dx, "conv2d_bwd_input: null pointer");
+    MTA_REQUIRE(dy != dx, "conv2d_bwd_input: in-place operation is not supported");
+    if (int rc = check_device()) return rc;
+    return conv2d_bwd_input_launch(dy, w, w_dtype, dx, (long)N * C, C, H, W, R, S, causal ? 1 : 0, dtype,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+size_t mta_conv2d_bwd_weight_workspace_bytes(int N, int C, int H, int W, int R, int S) {
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || R < 1 || S < 1) return 0;
+    return conv2d_bwd_weight_workspace(N, C, H, W, R, S);
+}
+
+int mta_conv2d_bwd_weight(const void* x, const void* dy, float* dw, void* workspace, size_t workspace_bytes, int N, int C,
+                          int H, int W, int R, int S, int causal, int dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(dtype), "conv2d_bwd_weight: unknown dtype code %d", dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && H >= 0 && W >= 0, "conv2d_bwd_weight: bad shape N=%d C=%d H=%d W=%d", N, C, H, W);
+    MTA_REQUIRE(R >= 1 && S >= 1, "conv2d_bwd_weight: kernel size %dx%d must be positive", R, S);
+    MTA_REQUIRE(dw, "conv2d_bwd_weight: null pointer");
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((long)N * H * W == 0) {
+        MTA_CUDA_OK(cudaMemsetAsync(dw, 0, (size_t)C * R * S * sizeof(float), st));
+        return MTA_OK;
+    }
+    MTA_REQUIRE(x && dy, "conv2d_bwd_weight: null pointer");
+    const size_t need = conv2d_bwd_weight_workspace(N, C, H, W, R, S);
+    MTA_REQUIRE(workspace && workspace_bytes >= need, "conv2d_bwd_weight: workspace of %zu bytes is smaller than the %zu needed",
+                workspace_bytes, need);
+    return conv2d_bwd_weight_launch(x, dy, dw, workspace, N, C, H, W, R, S, causal ? 1 : 0, dtype, st);
+}
+
+int mta_head_linear_bwd_input(const void* dy, const void* Wm, void* dx, int N, int C, int P, int Q, int causal, int dtype,
+                              int w_dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "head_linear_bwd_input: unknown dtype code (dy %d, w %d)", dtype, w_dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && P >= 0 && Q >= 0, "head_linear_bwd_input: bad shape N=%d C=%d P=%d Q=%d", N, C, P, Q);
+    if ((long)N * P * Q == 0) return MTA_OK;
+    MTA_REQUIRE(dy && Wm && dx, "head_linear_bwd_input: null pointer");
+    MTA_REQUIRE(dy != dx, "head_linear_bwd_input: in-place operation is not supported");
+    if (int rc = check_device()) return rc;
+    const PlaneView v = full_view(P, Q);
+    return head_linear_launch(dy, v, Wm, w_dtype, dx, v, N, C, P, Q, causal ? 1 : 0, 0.0f, 0, P, true, dtype,
+                              static_cast<cudaStream_t>(stream), true);
+}
+
+size_t mta_head_linear_bwd_weight_workspace_bytes(int C) {
+    if (C < 1 || C > 128) return 0;
+    return head_linear_bwd_weight_workspace(C);
+}
+
+int mta_head_linear_bwd_weight(const void* x, const void* dy, float* dW, void* workspace, size_t workspace_bytes, int N,
+                               int C, int P, int Q, int causal, int dtype, void* stream) {
+    g_error[0] = 0;
+    MTA_REQUIRE(dtype_ok(dtype), "head_linear_bwd_weight: unknown dtype code %d", dtype);
+    MTA_REQUIRE(N >= 0 && C >= 1 && C <= 128 && P >= 0 && Q >= 0, "head_linear_bwd_weight: bad shape N=%d C=%d P=%d Q=%d", N, C, P, Q);
+    MTA_REQUIRE(dW, "head_linear_bwd_weight: null pointer");
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((long)N * P * Q == 0) {
+        MTA_CUDA_OK(cudaMemsetAsync(dW, 0, (size_t)C * C * sizeof(float), st));
+        return MTA_OK;
+    }
+    MTA_REQUIRE(x && dy, "head_linear_bwd_weight: null pointer");
+    const size_t need = head_linear_bwd_weight_workspace(C);
+    MTA_REQUIRE(workspace && workspace_bytes >= need, "head_linear_bwd_weight: workspace of %zu bytes is smaller than the %zu needed",
+                workspace_bytes, need);
+    return head_linear_bwd_weight_launch(x, dy, dW, workspace, N, C, P, Q, causal ? 1 : 0, dtype, st);
+}
+
 int mta_qk_scores_fwd(const void* q, const void* k, void* s, int B, int H, int S, int D, float scale, int round_scale,
                       int causal, int dtype, void* stream) {
     g_error[0] = 0;

@@ -24,9 +24,12 @@ template <typename T>
 __global__ void __launch_bounds__(NTHREADS)
 conv2d_tile_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ w, int w_dtype,
                    T* __restrict__ y, PlaneView yv, int C, int H, int W, int R, int S, int causal,
-                   int row_begin, int row_end, int write_upper, int tiles_n) {
+                   int row_begin, int row_end, int write_upper, int tiles_n, int grad_input) {
     extern __shared__ float smem[];
-    const int pad_h = R - 1, pad_w = (S - 1) / 2;
+    // grad_input: the same kernel evaluates the gradient with respect to the conv's input (conv_bwd_input_kernel,
+    // convolution_2d_trit.py:143-218): dx[q,k] = sum_{i,j} w[R-1-i, S-1-j] * dyh[q + i, k + j - (S-1-pad_w)], i.e. the
+    // taps reversed, the rows looking forward instead of back, dyh masked like the forward's input
+    const int pad_h = grad_input ? 0 : R - 1, pad_w = grad_input ? S - 1 - (S - 1) / 2 : (S - 1) / 2;
     const int tw = TN + S - 1;                 // staged tile width
     const int th = TM + R - 1;                 // staged tile height
     float* xs = smem;                          // th x tw
@@ -50,7 +53,8 @@ conv2d_tile_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict
     }
 
     const int c = (int)(plane % C);
-    for (int idx = tid; idx < R * S; idx += NTHREADS) ws[idx] = load_weight(w, (long)c * R * S + idx, w_dtype);
+    for (int idx = tid; idx < R * S; idx += NTHREADS)
+        ws[idx] = load_weight(w, (long)c * R * S + (grad_input ? R * S - 1 - idx : idx), w_dtype);
     const T* xp = x + plane * xv.plane_stride;
     for (int idx = tid; idx < th * tw; idx += NTHREADS) {
         const int rr = idx / tw, cc = idx - rr * tw;
@@ -101,7 +105,7 @@ conv2d_tile_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict
 template <typename T>
 int launch_tile(const void* x, PlaneView xv, const void* w, int w_dtype, void* y, PlaneView yv, long planes, int C,
                 int H, int W, int R, int S, int causal, int row_begin, int row_end, bool write_upper,
-                cudaStream_t st) {
+                cudaStream_t st, bool grad_input = false) {
     const int tiles_m = (row_end - row_begin + TM - 1) / TM, tiles_n = (W + TN - 1) / TN;
     const size_t smem = ((size_t)(TM + R - 1) * (TN + S - 1) + (size_t)R * S) * sizeof(float);
     MTA_REQUIRE(smem <= 200 * 1024, "conv2d: kernel %dx%d needs %zu bytes of shared memory (max 204800)", R, S, smem);
@@ -111,7 +115,7 @@ int launch_tile(const void* x, PlaneView xv, const void* w, int w_dtype, void* y
     dim3 grid((unsigned)(tiles_m * tiles_n), (unsigned)planes);
     conv2d_tile_kernel<T><<<grid, NTHREADS, smem, st>>>(static_cast<const T*>(x), xv, w, w_dtype, static_cast<T*>(y), yv,
                                                          C, H, W, R, S, causal, row_begin, row_end, write_upper ? 1 : 0,
-                                                         tiles_n);
+                                                         tiles_n, grad_input ? 1 : 0);
     MTA_LAUNCH_OK("conv2d_tile_kernel");
     return MTA_OK;
 }
@@ -138,6 +142,18 @@ int conv2d_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w
         case MTA_F32: return launch_tile<float>(x, xv, w, w_dtype, y, yv, planes, C, H, W, R, S, causal, row_begin, row_end, write_upper, st);
         case MTA_BF16: return launch_tile<__nv_bfloat16>(x, xv, w, w_dtype, y, yv, planes, C, H, W, R, S, causal, row_begin, row_end, write_upper, st);
         default: return launch_tile<__half>(x, xv, w, w_dtype, y, yv, planes, C, H, W, R, S, causal, row_begin, row_end, write_upper, st);
+    }
+}
+
+// Gradient with respect to the conv's input, full planes: dx has the layout of x, zeros above the diagonal when causal.
+int conv2d_bwd_input_launch(const void* dy, const void* w, int w_dtype, void* dx, long planes, int C, int H, int W, int R,
+                            int S, int causal, int dtype, cudaStream_t st) {
+    if (planes == 0 || H == 0 || W == 0) return MTA_OK;
+    const PlaneView v{(long)H * W, 0, W};
+    switch (dtype) {
+        case MTA_F32: return launch_tile<float>(dy, v, w, w_dtype, dx, v, planes, C, H, W, R, S, causal, 0, H, true, st, true);
+        case MTA_BF16: return launch_tile<__nv_bfloat16>(dy, v, w, w_dtype, dx, v, planes, C, H, W, R, S, causal, 0, H, true, st, true);
+        default: return launch_tile<__half>(dy, v, w, w_dtype, dx, v, planes, C, H, W, R, S, causal, 0, H, true, st, true);
     }
 }
 

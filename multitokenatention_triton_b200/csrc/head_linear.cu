@@ -23,9 +23,10 @@ template <typename T, int CP>
 __global__ void __launch_bounds__(256)
 head_linear_simt_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
                         T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
-                        int write_upper) {
+                        int write_upper, int w_transposed) {
     extern __shared__ float ws[];   // C x C
-    for (int i = threadIdx.x; i < C * C; i += blockDim.x) ws[i] = load_weight(Wm, i, w_dtype);
+    for (int i = threadIdx.x; i < C * C; i += blockDim.x)
+        ws[i] = load_weight(Wm, w_transposed ? (long)(i % C) * C + i / C : i, w_dtype);
     __syncthreads();
     const int p = row_begin + blockIdx.y;
     const int q = blockIdx.x * blockDim.x + threadIdx.x;
@@ -133,7 +134,7 @@ template <typename T, int CP, bool SPLITW>
 __global__ void __launch_bounds__(MMA_WARPS * 32)
 head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
                        T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
-                       int row_end, int rows_per_cta, int write_upper) {
+                       int row_end, int rows_per_cta, int write_upper, int w_transposed) {
     constexpr int KSTEPS = CP / 8;
     constexpr int MT = (CP + 15) / 16;
     constexpr int NLOAD = CP / 4;            // head planes read per lane: t, t+4, ...
@@ -152,7 +153,7 @@ head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __rest
             for (int r = 0; r < 4; ++r) {
                 const int o = 16 * mt + g + ((r & 1) ? 8 : 0);
                 const int h = 8 * ks + t + ((r & 2) ? 4 : 0);
-                const float v = (o < C && h < C) ? load_weight(Wm, (long)o * C + h, w_dtype) : 0.0f;
+                const float v = (o < C && h < C) ? load_weight(Wm, w_transposed ? (long)h * C + o : (long)o * C + h, w_dtype) : 0.0f;
                 if (SPLITW) {
                     const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
                     wa[mt][ks][r] = hi;
@@ -670,22 +671,22 @@ int launch_mix_softmax(const void* x, PlaneView xv, const void* Wm, int w_dtype,
 
 template <typename T, int CP>
 int launch_simt(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
-                int causal, float fill, int row_begin, int row_end, bool write_upper, cudaStream_t st) {
+                int causal, float fill, int row_begin, int row_end, bool write_upper, bool wt, cudaStream_t st) {
     dim3 grid((unsigned)((Q + 255) / 256), (unsigned)(row_end - row_begin), (unsigned)N);
     const size_t smem = (size_t)C * C * sizeof(float);
     if (smem > 48 * 1024)
         MTA_CUDA_OK(cudaFuncSetAttribute(head_linear_simt_kernel<T, CP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     head_linear_simt_kernel<T, CP><<<grid, 256, smem, st>>>(static_cast<const T*>(x), xv, Wm, w_dtype, static_cast<T*>(y),
-                                                            yv, C, Q, causal, fill, row_begin, write_upper ? 1 : 0);
+                                                            yv, C, Q, causal, fill, row_begin, write_upper ? 1 : 0, wt ? 1 : 0);
     MTA_LAUNCH_OK("head_linear_simt_kernel");
     return MTA_OK;
 }
 
 template <typename T>
 int dispatch_simt(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
-                  int causal, float fill, int row_begin, int row_end, bool write_upper, cudaStream_t st) {
+                  int causal, float fill, int row_begin, int row_end, bool write_upper, bool wt, cudaStream_t st) {
 #define MTA_SIMT_CASE(CPV) \
-    return launch_simt<T, CPV>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, st)
+    return launch_simt<T, CPV>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st)
     if (C <= 8) MTA_SIMT_CASE(8);
     if (C <= 16) MTA_SIMT_CASE(16);
     if (C <= 32) MTA_SIMT_CASE(32);
@@ -696,7 +697,7 @@ int dispatch_simt(const void* x, PlaneView xv, const void* Wm, int w_dtype, void
 
 template <typename T, int CP>
 int launch_mma(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
-               int causal, float fill, int row_begin, int row_end, bool write_upper, cudaStream_t st) {
+               int causal, float fill, int row_begin, int row_end, bool write_upper, bool wt, cudaStream_t st) {
     const int rows = row_end - row_begin;
     const int rows_per_cta = rows >= 2048 ? 8 : (rows >= 256 ? 4 : 1);
     dim3 grid((unsigned)((Q + MMA_WARPS * MMA_KEYS_PER_WARP - 1) / (MMA_WARPS * MMA_KEYS_PER_WARP)),
@@ -704,20 +705,20 @@ int launch_mma(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y
     if (w_dtype == MTA_F32)
         head_linear_mma_kernel<T, CP, true><<<grid, MMA_WARPS * 32, 0, st>>>(
             static_cast<const T*>(x), xv, Wm, w_dtype, static_cast<T*>(y), yv, C, Q, causal, fill, row_begin, row_end,
-            rows_per_cta, write_upper ? 1 : 0);
+            rows_per_cta, write_upper ? 1 : 0, wt ? 1 : 0);
     else
         head_linear_mma_kernel<T, CP, false><<<grid, MMA_WARPS * 32, 0, st>>>(
             static_cast<const T*>(x), xv, Wm, w_dtype, static_cast<T*>(y), yv, C, Q, causal, fill, row_begin, row_end,
-            rows_per_cta, write_upper ? 1 : 0);
+            rows_per_cta, write_upper ? 1 : 0, wt ? 1 : 0);
     MTA_LAUNCH_OK("head_linear_mma_kernel");
     return MTA_OK;
 }
 
 template <typename T>
 int dispatch_mma(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
-                 int causal, float fill, int row_begin, int row_end, bool write_upper, cudaStream_t st) {
+                 int causal, float fill, int row_begin, int row_end, bool write_upper, bool wt, cudaStream_t st) {
 #define MTA_MMA_CASE(CPV) \
-    return launch_mma<T, CPV>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, st)
+    return launch_mma<T, CPV>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st)
     if (C <= 8) MTA_MMA_CASE(8);
     if (C <= 16) MTA_MMA_CASE(16);
     MTA_MMA_CASE(32);
@@ -754,7 +755,7 @@ int head_mix_softmax_launch(const void* x, PlaneView xv, const void* Wm, int w_d
 
 int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C,
                        int P, int Q, int causal, float fill, int row_begin, int row_end, bool write_upper, int dtype,
-                       cudaStream_t st) {
+                       cudaStream_t st, bool wt) {
     (void)P;
     if (N == 0 || row_end <= row_begin || Q == 0) return MTA_OK;
     MTA_REQUIRE(C >= 1 && C <= 128, "head_linear: C = %d heads is outside the supported range 1..128", C);
@@ -764,12 +765,12 @@ int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype,
     MTA_REQUIRE(want != 2 || mma_able, "head_linear: the tensor-core variant needs a 16-bit dtype, C <= 32, Q %% 8 == 0 and 16-byte aligned rows");
     const bool use_mma = mma_able && want != 1;
     if (dtype == MTA_F32)
-        return dispatch_simt<float>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, st);
+        return dispatch_simt<float>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st);
     if (dtype == MTA_BF16)
-        return use_mma ? dispatch_mma<__nv_bfloat16>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, st)
-                       : dispatch_simt<__nv_bfloat16>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, st);
-    return use_mma ? dispatch_mma<__half>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, st)
-                   : dispatch_simt<__half>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, st);
+        return use_mma ? dispatch_mma<__nv_bfloat16>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st)
+                       : dispatch_simt<__nv_bfloat16>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st);
+    return use_mma ? dispatch_mma<__half>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st)
+                   : dispatch_simt<__half>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st);
 }
 
 }  // namespace mta

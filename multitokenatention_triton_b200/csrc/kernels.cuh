@@ -20,9 +20,21 @@ int conv2d_mma_launch(const void* x, PlaneView xv, long x_rows_stored, const voi
                       bool write_upper, int dtype, cudaStream_t st);
 
 // Head mix over groups of C planes; rows [row_begin,row_end).  `write_upper` as above (value `fill`).
+// `w_transposed`: y[o] = sum_h Wm[h,o] x[h] (the gradient with respect to the head mix's input).
 int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N,
                        int C, int P, int Q, int causal, float fill, int row_begin, int row_end, bool write_upper,
-                       int dtype, cudaStream_t st);
+                       int dtype, cudaStream_t st, bool w_transposed = false);
+
+// Gradients of the two stand-alone ops (backward.cu, conv2d.cu).  dx of the conv: layout of x, zeros above the diagonal
+// when causal.  The weight gradients are float32, reduced in a fixed order through a caller workspace of the given size.
+int conv2d_bwd_input_launch(const void* dy, const void* w, int w_dtype, void* dx, long planes, int C, int H, int W, int R,
+                            int S, int causal, int dtype, cudaStream_t st);
+size_t conv2d_bwd_weight_workspace(int N, int C, int H, int W, int R, int S);
+int conv2d_bwd_weight_launch(const void* x, const void* dy, float* dw, void* workspace, int N, int C, int H, int W, int R,
+                             int S, int causal, int dtype, cudaStream_t st);
+size_t head_linear_bwd_weight_workspace(int C);
+int head_linear_bwd_weight_launch(const void* x, const void* dy, float* dW, void* workspace, int N, int C, int P, int Q,
+                                  int causal, int dtype, cudaStream_t st);
 
 // Head mix followed by the causal row softmax of the mixed logits, in one pass (16-bit dtypes, C <= 32, causal);
 // entries above the diagonal of y are written as 0 when `write_upper`, else left untouched.

@@ -2,7 +2,8 @@
 
 Mirrors TritonLinearHeadFunction / TritonLinearHead (triton_linear_head.py:281-401): weight (H,H) in
 nn.Linear orientation, `causal`, and `output_value` written above the diagonal.  The forward runs the
-CUDA kernel behind mta_head_linear_fwd.
+CUDA kernel behind mta_head_linear_fwd, the backward those behind mta_head_linear_bwd_input /
+mta_head_linear_bwd_weight.
 """
 import torch
 import torch.nn as nn
@@ -13,11 +14,21 @@ from . import ops
 class TritonLinearHeadFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, weight, causal=True, output_value=0.0):
+        ctx.save_for_backward(input, weight)
+        ctx.causal = causal
         return ops.head_linear_fwd(input, weight, causal, output_value)
 
     @staticmethod
     def backward(ctx, grad_output):
-        raise NotImplementedError("the B200 MTA library implements the forward pass only")
+        # the reference's backward (triton_linear_head.py:321-370); entries above the diagonal carry no gradient
+        input, weight = ctx.saved_tensors
+        grad_input = grad_weight = None
+        grad_output = grad_output.to(input.dtype)
+        if ctx.needs_input_grad[0]:
+            grad_input = ops.head_linear_bwd_input(grad_output, weight, ctx.causal)
+        if ctx.needs_input_grad[1]:
+            grad_weight = ops.head_linear_bwd_weight(input, grad_output, ctx.causal).to(weight.dtype)
+        return grad_input, grad_weight, None, None
 
 
 class TritonLinearHead(nn.Module):

@@ -60,6 +60,66 @@ def head_linear_fwd(x: torch.Tensor, weight: torch.Tensor, causal: bool = True, 
     return y
 
 
+def conv2d_bwd_input(grad_output: torch.Tensor, weight: torch.Tensor, causal: bool) -> torch.Tensor:
+    """Gradient of conv2d_fwd with respect to its input: (N,C,H,W), zeros above the diagonal when causal."""
+    g = _cuda_contig(grad_output, "grad_output")
+    N, C, H, W = g.shape
+    Cw, R, S = weight.shape
+    assert C == Cw, "This implementation assumes depthwise convolution (C_in == C_out)"
+    w = _weight(weight, g, "weight")
+    dx = torch.empty_like(g)
+    with torch.cuda.device(g.device):
+        check(lib().mta_conv2d_bwd_input(g.data_ptr(), w.data_ptr(), dx.data_ptr(), N, C, H, W, R, S, int(bool(causal)),
+                                         dtype_code(g), dtype_code(w), stream_ptr(g.device)), "mta_conv2d_bwd_input")
+    return dx
+
+
+def conv2d_bwd_weight(x: torch.Tensor, grad_output: torch.Tensor, kernel_size: Tuple[int, int], causal: bool) -> torch.Tensor:
+    """Gradient of conv2d_fwd with respect to its weight: (C,R,S) float32."""
+    x, g = _cuda_contig(x, "input"), _cuda_contig(grad_output, "grad_output")
+    assert x.shape == g.shape and x.dtype == g.dtype
+    N, C, H, W = x.shape
+    R, S = kernel_size
+    dw = torch.empty(C, R, S, device=x.device, dtype=torch.float32)
+    L = lib()
+    nbytes = L.mta_conv2d_bwd_weight_workspace_bytes(N, C, H, W, R, S)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(L.mta_conv2d_bwd_weight(x.data_ptr(), g.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws.numel(), N, C, H, W, R, S,
+                                      int(bool(causal)), dtype_code(x), stream_ptr(x.device)), "mta_conv2d_bwd_weight")
+    return dw
+
+
+def head_linear_bwd_input(grad_output: torch.Tensor, weight: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """Gradient of head_linear_fwd with respect to its input: sum_o W[o,h] dy[o]; zeros above the diagonal when causal."""
+    g = _cuda_contig(grad_output, "grad_output")
+    N, C, P, Q = g.shape
+    assert weight.shape == (C, C), f"Weight must be a ({C},{C}) matrix, got {tuple(weight.shape)}"
+    w = _weight(weight, g, "weight")
+    dx = torch.empty_like(g)
+    with torch.cuda.device(g.device):
+        check(lib().mta_head_linear_bwd_input(g.data_ptr(), w.data_ptr(), dx.data_ptr(), N, C, P, Q, int(bool(causal)),
+                                              dtype_code(g), dtype_code(w), stream_ptr(g.device)), "mta_head_linear_bwd_input")
+    return dx
+
+
+def head_linear_bwd_weight(x: torch.Tensor, grad_output: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """Gradient of head_linear_fwd with respect to its weight: (C,C) float32."""
+    x, g = _cuda_contig(x, "input"), _cuda_contig(grad_output, "grad_output")
+    assert x.shape == g.shape and x.dtype == g.dtype
+    N, C, P, Q = x.shape
+    dW = torch.empty(C, C, device=x.device, dtype=torch.float32)
+    L = lib()
+    nbytes = L.mta_head_linear_bwd_weight_workspace_bytes(C)
+    if nbytes == 0:
+        raise MTALibraryError(f"head_linear_bwd_weight: C = {C} heads is outside the supported range 1..128")
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(L.mta_head_linear_bwd_weight(x.data_ptr(), g.data_ptr(), dW.data_ptr(), ws.data_ptr(), ws.numel(), N, C, P, Q,
+                                           int(bool(causal)), dtype_code(x), stream_ptr(x.device)), "mta_head_linear_bwd_weight")
+    return dW
+
+
 def head_linear_softmax_fwd(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """Causal head mix then row softmax of the mixed logits in one pass: x (N,C,P,Q), weight (C,C) -> probabilities
     (N,C,P,Q), zero above the diagonal.  Equals softmax_fwd(head_linear_fwd(x, weight, True, -inf)) up to the order of

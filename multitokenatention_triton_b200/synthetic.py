@@ -122,3 +122,9 @@ def make_head_linear_inputs(N: int, C: int, S: int, dtype: torch.dtype, seed: in
         logits = torch.randn(C, S, S, generator=g) + mask
         x[n] = torch.softmax(logits, dim=-1)
     return {"x": x.to(dtype), "W": W.to(dtype)}
+
+
+def make_upstream_grad(shape, dtype: torch.dtype, seed: int) -> torch.Tensor:
+    """Seeded upstream gradient for the backward checks: N(0,1) drawn in float32 on the CPU, cast to `dtype`."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randn(*shape, generator=g).to(dtype)

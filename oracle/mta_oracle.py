@@ -39,6 +39,11 @@ def lib() -> ctypes.CDLL:
         L.mta_oracle_conv2d.argtypes = [fp, fp, fp, i, i, i, i, i, i, i, i]
         L.mta_oracle_head_linear.argtypes = [fp, fp, fp, i, i, i, i, i, ctypes.c_float, i]
         L.mta_oracle_softmax.argtypes = [fp, fp, ctypes.c_long, i, i, i, i]
+        dp = ctypes.POINTER(ctypes.c_double)
+        L.mta_oracle_conv2d_bwd_input.argtypes = [fp, fp, fp, i, i, i, i, i, i, i, i]
+        L.mta_oracle_conv2d_bwd_weight.argtypes = [fp, fp, dp, i, i, i, i, i, i, i]
+        L.mta_oracle_head_linear_bwd_input.argtypes = [fp, fp, fp, i, i, i, i, i, i]
+        L.mta_oracle_head_linear_bwd_weight.argtypes = [fp, fp, dp, i, i, i, i, i]
         L.mta_oracle_round.argtypes = [fp, fp, ctypes.c_long, i]
         L.mta_oracle_mta_fwd_rows.argtypes = [fp] * 7 + [i] * 13 + [fp]
         L.mta_oracle_conv_attn_fwd_rows.argtypes = [fp] * 4 + [i] * 7 + [ctypes.c_float] + [i] * 4 + [fp]
@@ -99,6 +104,47 @@ def head_linear(x, Wm, causal: bool = True, fill: float = 0.0, round_mode: int =
     _check(lib().mta_oracle_head_linear(_p(x), _p(Wm), _p(y), N, C, P, Q, int(causal), float(fill), round_mode),
            "head_linear")
     return y
+
+
+def _pd(a: np.ndarray):
+    return a.ctypes.data_as(ctypes.POINTER(ctypes.c_double))
+
+
+def conv2d_bwd_input(dy, w, causal: bool, round_mode: int = ROUND_NONE) -> np.ndarray:
+    """Gradient of conv2d with respect to its input; dy (N,C,H,W), w (C,R,S)."""
+    dy, w = _f32(dy), _f32(w)
+    N, C, H, W = dy.shape
+    _, R, S = w.shape
+    dx = np.empty_like(dy)
+    _check(lib().mta_oracle_conv2d_bwd_input(_p(dy), _p(w), _p(dx), N, C, H, W, R, S, int(causal), round_mode), "conv2d_bwd_input")
+    return dx
+
+
+def conv2d_bwd_weight(x, dy, kernel_size, causal: bool) -> np.ndarray:
+    """Gradient of conv2d with respect to its weight, float64 (C,R,S)."""
+    x, dy = _f32(x), _f32(dy)
+    N, C, H, W = x.shape
+    R, S = kernel_size
+    dw = np.empty((C, R, S), dtype=np.float64)
+    _check(lib().mta_oracle_conv2d_bwd_weight(_p(x), _p(dy), _pd(dw), N, C, H, W, R, S, int(causal)), "conv2d_bwd_weight")
+    return dw
+
+
+def head_linear_bwd_input(dy, Wm, causal: bool = True, round_mode: int = ROUND_NONE) -> np.ndarray:
+    dy, Wm = _f32(dy), _f32(Wm)
+    N, C, P, Q = dy.shape
+    dx = np.empty_like(dy)
+    _check(lib().mta_oracle_head_linear_bwd_input(_p(dy), _p(Wm), _p(dx), N, C, P, Q, int(causal), round_mode),
+           "head_linear_bwd_input")
+    return dx
+
+
+def head_linear_bwd_weight(x, dy, causal: bool = True) -> np.ndarray:
+    x, dy = _f32(x), _f32(dy)
+    N, C, P, Q = x.shape
+    dW = np.empty((C, C), dtype=np.float64)
+    _check(lib().mta_oracle_head_linear_bwd_weight(_p(x), _p(dy), _pd(dW), N, C, P, Q, int(causal)), "head_linear_bwd_weight")
+    return dW
 
 
 def softmax(x, causal: bool = True, round_mode: int = ROUND_NONE) -> np.ndarray:

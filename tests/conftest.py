@@ -17,3 +17,9 @@ def pytest_configure(config):
 def golden():
     from cases import load_golden
     return load_golden()
+
+
+@pytest.fixture(scope="session")
+def golden_bwd():
+    from cases import BACKWARD_GOLDEN, load_golden
+    return load_golden(os.path.join(ROOT, "tests", "golden", BACKWARD_GOLDEN))

@@ -61,6 +61,12 @@ CONV_ATTN_CASES = {
 }
 
 
+# Backward cases: subsets of the tables above; the upstream gradient is make_upstream_grad(shape, dtype, seed + 1000).
+CONV_BWD_CASES = ["s1", "s5_3x3", "s63_3x5", "s64_6x11", "s65_6x11", "s130_5x7_noncausal", "s64_6x11_noncausal"]
+HEAD_BWD_CASES = ["s1_h1", "s5_h3", "s63_h8", "s64_h16", "s65_h16", "s193_h5", "s64_h16_noncausal"]
+BACKWARD_GOLDEN = "golden_backward.npz"
+
+
 def load_golden(path=None):
     """name -> float32 numpy array.  16-bit outputs are stored as bit patterns under 'name@bf16' / 'name@f16'."""
     import numpy as np
