@@ -25,15 +25,17 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 constexpr int WT_M = 32, WT_N = 128, WT_CPT = 8;
 constexpr int WT_THREADS = WT_M * (WT_N / WT_CPT) / 2;     // 256: a thread owns 2 rows x 8 columns of output positions
 
-template <typename T>
+// SC = the key extent when it is one of the common sizes (the window of a row tap then sits in registers and every tap
+// indexes it statically), 0 = any size (the window is re-read from shared memory per tap).
+template <typename T, int SC>
 __global__ void __launch_bounds__(WT_THREADS)
 conv2d_bwd_weight_kernel(const T* __restrict__ x, const T* __restrict__ dy, float* __restrict__ partial, int H, int W,
                          int R, int S, int causal, int tiles_n) {
     extern __shared__ __align__(16) float smem[];
     const int pad_h = R - 1, pad_w = (S - 1) / 2;
-    const int tw = WT_N + S - 1, th = WT_M + R - 1;
+    const int tw = (WT_N + S - 1 + 3) & ~3, th = WT_M + R - 1;      // row pitch a multiple of 4 floats: 16-byte window loads
     float* xs = smem;                               // th x tw, masked input
-    float* part = smem + th * tw;                   // (WT_THREADS / 32) x R*S warp partials
+    float* part = smem + th * tw + 8;               // (WT_THREADS / 32) x R*S warp partials
     const long plane = blockIdx.y;
     const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
     const int m0 = tile_m * WT_M, n0 = tile_n * WT_N;
@@ -66,12 +68,31 @@ conv2d_bwd_weight_kernel(const T* __restrict__ x, const T* __restrict__ dy, floa
     for (int i = 0; i < R; ++i) {
         const float* r0 = xs + (ry + i) * tw + cx;
         const float* r1 = xs + (ry + WT_M / 2 + i) * tw + cx;
-        for (int j = 0; j < S; ++j) {
-            float v = 0.0f;
+        if constexpr (SC > 0) {
+            constexpr int WIN = (WT_CPT + SC - 1 + 3) & ~3;
+            float w0[WIN], w1[WIN];
 #pragma unroll
-            for (int e = 0; e < WT_CPT; ++e) v = fmaf(r0[j + e], g0[e], fmaf(r1[j + e], g1[e], v));
-            v = warp_sum_f(v);
-            if (lane == 0) part[warp * taps + i * S + j] = v;
+            for (int c4 = 0; c4 < WIN / 4; ++c4) {
+                const float4 a = reinterpret_cast<const float4*>(r0)[c4], b = reinterpret_cast<const float4*>(r1)[c4];
+                w0[4 * c4] = a.x; w0[4 * c4 + 1] = a.y; w0[4 * c4 + 2] = a.z; w0[4 * c4 + 3] = a.w;
+                w1[4 * c4] = b.x; w1[4 * c4 + 1] = b.y; w1[4 * c4 + 2] = b.z; w1[4 * c4 + 3] = b.w;
+            }
+#pragma unroll
+            for (int j = 0; j < SC; ++j) {
+                float v = 0.0f;
+#pragma unroll
+                for (int e = 0; e < WT_CPT; ++e) v = fmaf(w0[j + e], g0[e], fmaf(w1[j + e], g1[e], v));
+                v = warp_sum_f(v);
+                if (lane == 0) part[warp * taps + i * SC + j] = v;
+            }
+        } else {
+            for (int j = 0; j < S; ++j) {
+                float v = 0.0f;
+#pragma unroll
+                for (int e = 0; e < WT_CPT; ++e) v = fmaf(r0[j + e], g0[e], fmaf(r1[j + e], g1[e], v));
+                v = warp_sum_f(v);
+                if (lane == 0) part[warp * taps + i * S + j] = v;
+            }
         }
     }
     __syncthreads();
@@ -159,6 +180,112 @@ head_linear_bwd_weight_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     }
 }
 
+// Tensor-core version for 16-bit dtypes and C <= 32: dW = dY X^T with the positions as the contraction index of
+// mma.sync m16n8k16 (A = dy, rows = output heads; B = x, columns = input heads).  The contraction index may be
+// assigned to positions in any order as long as A and B agree, so lane (g,t) reads 16 bytes (8 consecutive keys
+// 8t .. 8t+7 of a 32-key group) from planes g and g+8 of dy and of x, and word w of those vectors feeds k-slots
+// {2t,2t+1} (w even) or {2t+8,2t+9} (w odd) of MMA w/2.  A warp owns (batch element, row, 128-key block) items and
+// accumulates over all of them in registers; MT = 16-head tiles per side.
+template <typename T> struct MmaK16;
+template <> struct MmaK16<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+};
+template <> struct MmaK16<__half> {
+    static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+};
+
+constexpr int HM_WARPS = 4;
+constexpr int HM_KEYS = 128;       // keys per item
+
+template <typename T, int MT>
+__global__ void __launch_bounds__(HM_WARPS * 32)
+head_linear_bwd_weight_mma_kernel(const T* __restrict__ x, const T* __restrict__ dy, float* __restrict__ partial, int N, int C,
+                                  int P, int Q, int causal) {
+    constexpr int CP = 16 * MT, NV = 2 * MT;            // padded heads; 16-byte vectors per lane, side and 32-key group
+    __shared__ float red[HM_WARPS][CP * CP];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    float acc[MT][2 * MT][4];                            // [16-row tile of o][8-column tile of h][fragment]
+#pragma unroll
+    for (int a = 0; a < MT; ++a)
+#pragma unroll
+        for (int b = 0; b < 2 * MT; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.0f;
+    const int kblocks = (Q + HM_KEYS - 1) / HM_KEYS;
+    const long items = (long)N * P * kblocks;
+    const long plane = (long)P * Q;
+    for (long item = (long)blockIdx.x * HM_WARPS + warp; item < items; item += (long)gridDim.x * HM_WARPS) {
+        const int kb = (int)(item % kblocks);
+        const int p = (int)((item / kblocks) % P);
+        const long n = item / ((long)kblocks * P);
+        const int k0 = kb * HM_KEYS;
+        if (causal && k0 > p) continue;
+        const int n_keys = causal ? min(p + 1, Q) : Q;   // keys of this row that carry a gradient
+        const long row_off = n * C * plane + (long)p * Q;
+        uint4 gv[4][NV], xv[4][NV];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int kq = k0 + 32 * j + 8 * t;
+#pragma unroll
+            for (int r = 0; r < NV; ++r) {
+                const int head = g + 8 * r;
+                if (head < C && kq < n_keys) {
+                    gv[j][r] = __ldg(reinterpret_cast<const uint4*>(dy + row_off + head * plane + kq));
+                    xv[j][r] = __ldg(reinterpret_cast<const uint4*>(x + row_off + head * plane + kq));
+                } else {
+                    gv[j][r] = make_uint4(0u, 0u, 0u, 0u);
+                    xv[j][r] = make_uint4(0u, 0u, 0u, 0u);
+                }
+                if (kq + 8 > n_keys && kq < n_keys) {     // the vector that holds the last valid key: zero what lies beyond it
+                    uint32_t* wd = &gv[j][r].x;
+                    uint32_t* wx = &xv[j][r].x;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        if (kq + e >= n_keys) {
+                            wd[e >> 1] &= (e & 1) ? 0x0000ffffu : 0xffff0000u;
+                            wx[e >> 1] &= (e & 1) ? 0x0000ffffu : 0xffff0000u;
+                        }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int a = 0; a < MT; ++a)
+#pragma unroll
+                    for (int b = 0; b < 2 * MT; ++b) {
+                        const uint32_t* ga = &gv[j][2 * a].x;       // dy of head 16a + g
+                        const uint32_t* gb = &gv[j][2 * a + 1].x;   // dy of head 16a + g + 8
+                        const uint32_t* xb = &xv[j][b].x;           // x of head 8b + g
+                        MmaK16<T>::run(acc[a][b], ga[2 * m], gb[2 * m], ga[2 * m + 1], gb[2 * m + 1], xb[2 * m], xb[2 * m + 1]);
+                    }
+    }
+    // fragment (a, b): c0 c1 = (o = 16a + g, h = 8b + 2t, + 1), c2 c3 = (o + 8, same h)
+#pragma unroll
+    for (int a = 0; a < MT; ++a)
+#pragma unroll
+        for (int b = 0; b < 2 * MT; ++b)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int o = 16 * a + g + ((r & 2) ? 8 : 0), h = 8 * b + 2 * t + (r & 1);
+                red[warp][o * CP + h] = acc[a][b][r];
+            }
+    __syncthreads();
+    for (int i = threadIdx.x; i < CP * CP; i += HM_WARPS * 32) {
+        const int o = i / CP, h = i % CP;
+        if (o < C && h < C) partial[(long)blockIdx.x * C * C + o * C + h] = red[0][i] + red[1][i] + red[2][i] + red[3][i];
+    }
+}
+
 __global__ void head_linear_bwd_weight_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW, int ctas,
                                                      int pairs) {
     const int pair = blockIdx.x * blockDim.x + threadIdx.x;
@@ -202,21 +329,34 @@ int conv2d_bwd_weight_launch(const void* x, const void* dy, float* dw, void* wor
     const long planes = (long)N * C;
     MTA_REQUIRE(planes <= 65535, "conv2d_bwd_weight: N*C = %ld exceeds 65535", planes);
     const int taps = R * S;
-    const size_t smem = ((size_t)(WT_M + R - 1) * (WT_N + S - 1) + (size_t)(WT_THREADS / 32) * taps) * sizeof(float);
+    // rows padded to a multiple of 4 floats, plus slack for the last window's 16-byte over-read
+    const size_t smem = ((size_t)(WT_M + R - 1) * ((WT_N + S - 1 + 3) & ~3) + 8 + (size_t)(WT_THREADS / 32) * taps) * sizeof(float);
     MTA_REQUIRE(smem <= 200 * 1024, "conv2d_bwd_weight: kernel %dx%d needs %zu bytes of shared memory (max 204800)", R, S, smem);
     float* partial = static_cast<float*>(workspace);
     dim3 grid((unsigned)(tiles_m * tiles_n), (unsigned)planes);
-#define MTA_BW_CASE(TT)                                                                                                  \
+#define MTA_BW_LAUNCH(TT, SCV)                                                                                           \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
-            MTA_CUDA_OK(cudaFuncSetAttribute(conv2d_bwd_weight_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        conv2d_bwd_weight_kernel<TT><<<grid, WT_THREADS, smem, st>>>(static_cast<const TT*>(x), static_cast<const TT*>(dy), \
-                                                                     partial, H, W, R, S, causal, tiles_n);               \
+            MTA_CUDA_OK(cudaFuncSetAttribute(conv2d_bwd_weight_kernel<TT, SCV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        conv2d_bwd_weight_kernel<TT, SCV><<<grid, WT_THREADS, smem, st>>>(static_cast<const TT*>(x), static_cast<const TT*>(dy), \
+                                                                          partial, H, W, R, S, causal, tiles_n);          \
+    } while (0)
+#define MTA_BW_CASE(TT)                                     \
+    do {                                                    \
+        switch (S) {                                        \
+            case 3: MTA_BW_LAUNCH(TT, 3); break;            \
+            case 5: MTA_BW_LAUNCH(TT, 5); break;            \
+            case 7: MTA_BW_LAUNCH(TT, 7); break;            \
+            case 11: MTA_BW_LAUNCH(TT, 11); break;          \
+            case 15: MTA_BW_LAUNCH(TT, 15); break;          \
+            default: MTA_BW_LAUNCH(TT, 0); break;           \
+        }                                                   \
     } while (0)
     if (dtype == MTA_F32) MTA_BW_CASE(float);
     else if (dtype == MTA_BF16) MTA_BW_CASE(__nv_bfloat16);
     else MTA_BW_CASE(__half);
 #undef MTA_BW_CASE
+#undef MTA_BW_LAUNCH
     MTA_LAUNCH_OK("conv2d_bwd_weight_kernel");
     conv2d_bwd_weight_reduce_kernel<<<(unsigned)(C * taps), 256, 0, st>>>(partial, dw, N, C, tiles_m * tiles_n, taps);
     MTA_LAUNCH_OK("conv2d_bwd_weight_reduce_kernel");
@@ -238,7 +378,17 @@ int head_linear_bwd_weight_launch(const void* x, const void* dy, float* dW, void
     const int grid = hw_grid(sms);
     float* partial = static_cast<float*>(workspace);
     int rc;
-    if (dtype == MTA_F32) rc = dispatch_hw<float>(x, dy, partial, N, C, P, Q, causal, grid, st);
+    const bool vec_ok = dtype != MTA_F32 && C <= 32 && Q % 8 == 0 && aligned16(x) && aligned16(dy);
+    if (vec_ok && variant("head_linear") != 1) {         // tensor cores (mta_set_variant("head_linear", 1): CUDA cores)
+#define MTA_HM_CASE(TT, MTV)                                                                                              \
+    head_linear_bwd_weight_mma_kernel<TT, MTV><<<grid, HM_WARPS * 32, 0, st>>>(static_cast<const TT*>(x), static_cast<const TT*>(dy), \
+                                                                               partial, N, C, P, Q, causal)
+        if (dtype == MTA_BF16) { if (C <= 16) MTA_HM_CASE(__nv_bfloat16, 1); else MTA_HM_CASE(__nv_bfloat16, 2); }
+        else { if (C <= 16) MTA_HM_CASE(__half, 1); else MTA_HM_CASE(__half, 2); }
+#undef MTA_HM_CASE
+        MTA_LAUNCH_OK("head_linear_bwd_weight_mma_kernel");
+        rc = MTA_OK;
+    } else if (dtype == MTA_F32) rc = dispatch_hw<float>(x, dy, partial, N, C, P, Q, causal, grid, st);
     else if (dtype == MTA_BF16) rc = dispatch_hw<__nv_bfloat16>(x, dy, partial, N, C, P, Q, causal, grid, st);
     else rc = dispatch_hw<__half>(x, dy, partial, N, C, P, Q, causal, grid, st);
     if (rc) return rc;

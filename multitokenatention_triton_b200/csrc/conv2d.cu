@@ -150,6 +150,10 @@ int conv2d_bwd_input_launch(const void* dy, const void* w, int w_dtype, void* dx
                             int S, int causal, int dtype, cudaStream_t st) {
     if (planes == 0 || H == 0 || W == 0) return MTA_OK;
     const PlaneView v{(long)H * W, 0, W};
+    // 16-bit dtypes, small odd key extents: the tcgen05 conv kernel with the taps reversed (mta_set_variant("conv2d", 1)
+    // keeps it on the CUDA cores)
+    if (variant("conv2d") != 1 && S % 2 == 1 && planes <= 65535 && conv2d_tc05_supported(dy, v, dx, v, W, R, S, dtype, w_dtype))
+        return conv2d_tc05_launch(dy, v, H, w, w_dtype, dx, v, planes, C, H, W, R, S, causal, 0, H, true, dtype, st, true);
     switch (dtype) {
         case MTA_F32: return launch_tile<float>(dy, v, w, w_dtype, dx, v, planes, C, H, W, R, S, causal, 0, H, true, st, true);
         case MTA_BF16: return launch_tile<__nv_bfloat16>(dy, v, w, w_dtype, dx, v, planes, C, H, W, R, S, causal, 0, H, true, st, true);

@@ -112,6 +112,9 @@ __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t saddr, uint32_t lbo
 
 struct ConvGeom {
     int C, W, R, S, causal, row_begin, row_end, tiles_n, tiles_m, x_row0, write_upper, split_w;
+    int lead;          // staged rows start `lead` rows before the tile: R-1 for the conv (row taps look back), 0 for its
+                       // input gradient (taps reversed, looking forward)
+    int flip;          // input gradient: tap (i, j) uses w[R-1-i][S-1-j]
     long tiles_per_plane, total_tiles;
     long zero_per_plane, zero_total;     // tiles wholly above the diagonal that must be written as zero (write_upper)
 };
@@ -259,9 +262,9 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 mbar_expect_tx(&full_bar[st], (uint32_t)(NBOX * TH * 128 + TH * 32));
 #pragma unroll
                 for (int j = 0; j < NBOX; ++j)
-                    tma_load_3d(xa + j * box_bytes, &mx, &full_bar[st], it.n0() - pad8 + 64 * j, it.m0(g) - (R - 1) - g.x_row0,
+                    tma_load_3d(xa + j * box_bytes, &mx, &full_bar[st], it.n0() - pad8 + 64 * j, it.m0(g) - g.lead - g.x_row0,
                                 it.plane);
-                tma_load_3d(xa + NBOX * box_bytes, &mx3, &full_bar[st], it.n0() - pad8 + 128, it.m0(g) - (R - 1) - g.x_row0, it.plane);
+                tma_load_3d(xa + NBOX * box_bytes, &mx3, &full_bar[st], it.n0() - pad8 + 128, it.m0(g) - g.lead - g.x_row0, it.plane);
                 *reinterpret_cast<volatile int*>(&tiles_loaded) = n + 1;
             }
             PROF_FLUSH(12, true)
@@ -367,7 +370,9 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                     const int i = idx / 512, e = idx % 512;
                     const int nn = e / 16, kk = e % 16;
                     const int j = kk + 16 - nn - a_off;
-                    const float wv = (j >= 0 && j < S) ? load_weight(w, ((long)head * R + i) * S + j, w_dtype) : 0.0f;
+                    const float wv = (j >= 0 && j < S) ? load_weight(w, g.flip ? ((long)head * R + (R - 1 - i)) * S + (S - 1 - j)
+                                                                             : ((long)head * R + i) * S + j, w_dtype)
+                                                       : 0.0f;
                     const T hi = from_f32<T>(wv);
                     const int off = i * 1024 + (kk / 8) * 512 + (nn / 8) * 128 + (nn % 8) * 16 + (kk % 8) * 2;
                     *reinterpret_cast<T*>(tb + off) = hi;
@@ -379,11 +384,11 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             PROF_ACC(6, warp == 2)
             // staged row sr is query m0-(R-1)+sr; staged column sc is key n0-pad8+sc, in box sc/64 at byte
             // sr*128 + (((sc%64)/8) ^ (sr%8))*16 + (sc%8)*2.  Zero the keys above the query.
-            if (g.causal && n0 - pad8 + NCH * 8 - 1 > m0 - (R - 1)) {
+            if (g.causal && n0 - pad8 + NCH * 8 - 1 > m0 - g.lead) {
                 // one thread per staged row: zero from the first key above the query to the end of the row
                 const int c0 = n0 - pad8;
                 for (int sr = ft; sr < TH; sr += 128) {
-                    const int qq = m0 - (R - 1) + sr;
+                    const int qq = m0 - g.lead + sr;
                     int first = qq - c0 + 1;                      // first staged column to zero
                     if (first >= NCH * 8) continue;
                     if (first < 0) first = 0;
@@ -490,7 +495,7 @@ size_t conv2d_tc05_smem_bytes(int R, bool split_w) {
 template <typename T>
 int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
                 long planes, int C, int W, int R, int S, int causal, int row_begin, int row_end, bool write_upper,
-                cudaStream_t st) {
+                bool grad_input, cudaStream_t st) {
     CUtensorMap mx;
     int rc;
     const int TH = TM + R - 1;
@@ -511,6 +516,8 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
     g.C = C; g.W = W; g.R = R; g.S = S; g.causal = causal; g.row_begin = row_begin; g.row_end = row_end;
     g.tiles_n = (W + TN - 1) / TN; g.x_row0 = xv.row0; g.write_upper = write_upper ? 1 : 0;
     g.split_w = w_dtype == MTA_F32 ? 1 : 0;
+    g.lead = grad_input ? 0 : R - 1;
+    g.flip = grad_input ? 1 : 0;
     const int tiles_m = (row_end - row_begin + TM - 1) / TM;
     g.tiles_m = tiles_m;
     long per_plane = 0;
@@ -558,13 +565,14 @@ bool conv2d_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView
 
 int conv2d_tc05_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
                        long planes, int C, int H, int W, int R, int S, int causal, int row_begin, int row_end,
-                       bool write_upper, int dtype, cudaStream_t st) {
+                       bool write_upper, int dtype, cudaStream_t st, bool grad_input) {
     (void)H;
+    MTA_REQUIRE(!grad_input || S % 2 == 1, "conv2d (tcgen05): the input gradient needs an odd key extent");
     if (dtype == MTA_BF16)
         return launch_tc05<__nv_bfloat16>(x, xv, x_rows_stored, w, w_dtype, y, yv, planes, C, W, R, S, causal, row_begin,
-                                          row_end, write_upper, st);
+                                          row_end, write_upper, grad_input, st);
     return launch_tc05<__half>(x, xv, x_rows_stored, w, w_dtype, y, yv, planes, C, W, R, S, causal, row_begin, row_end,
-                               write_upper, st);
+                               write_upper, grad_input, st);
 }
 
 }  // namespace mta

@@ -72,9 +72,11 @@ int conv_mix_launch(const void* x, PlaneView xv, long x_rows_stored, const void*
 // shared-memory rings (R <= 13 with 16-bit weights).
 bool conv2d_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int W, int R, int S, int dtype,
                            int w_dtype);
+// `grad_input` (odd S): the same kernel evaluates the gradient with respect to the conv's input - taps reversed, rows
+// looking forward - with x = dy and y = dx.
 int conv2d_tc05_launch(const void* x, PlaneView xv, long x_rows_stored, const void* w, int w_dtype, void* y, PlaneView yv,
                        long planes, int C, int H, int W, int R, int S, int causal, int row_begin, int row_end,
-                       bool write_upper, int dtype, cudaStream_t st);
+                       bool write_upper, int dtype, cudaStream_t st, bool grad_input = false);
 
 // tcgen05 tensor-core versions (gemm_tc05.cu): 16-bit dtypes, D in {64,128}, S a multiple of 8.
 bool tc05_contractions_supported(int S, int D, int dtype, const void* a, const void* b, const void* c, PlaneView view);

@@ -1,6 +1,6 @@
 """Micro-benchmarks of the stand-alone kernels on the configurations their roofline targets are quoted on.
 
-    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|mix_softmax|qk|pv|all] [--variant V]
+    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|mix_softmax|qk|pv|backward|all] [--variant V]
                                                         [--batch N] [--seq S] [--iters K]
 
   conv2d       causal depthwise conv 6x11 on a (B=4, H=16, S=2048, S) bf16 score plane
@@ -63,7 +63,7 @@ def _line(name, ms, nbytes=None, flops=None, **extra):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "mix_softmax", "qk", "pv", "all"])
+    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "mix_softmax", "qk", "pv", "backward", "all"])
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--heads", type=int, default=16)
@@ -117,6 +117,25 @@ def main():
             ms = _time(run, a.iters)
             _line(f"head mix {C}x{C} + softmax, one pass", ms, nbytes=es * N * C * (tri + S * S), shape=shape)
         del x, y
+    if a.which in ("backward", "all"):
+        # gradients of the two stand-alone ops: dx moves read-lower + write-full like the forward; a weight gradient
+        # reads the lower triangle of x and of dy
+        from .synthetic import make_upstream_grad
+        inp = make_conv_inputs(N, C, S, D, 6, 11, dtype, seed=1)
+        x, w = inp["x"].to(dev), inp["w"].to(dev)
+        g = make_upstream_grad((N, C, S, S), dtype, 1001).to(dev)
+        ms = _time(lambda: ops.conv2d_bwd_input(g, w, True), a.iters)
+        _line("conv2d 6x11 causal, input gradient", ms, nbytes=es * N * C * (tri + S * S), shape=shape, variant=a.variant)
+        ms = _time(lambda: ops.conv2d_bwd_weight(x, g, (6, 11), True), a.iters)
+        _line("conv2d 6x11 causal, weight gradient", ms, nbytes=2 * es * N * C * tri, shape=shape)
+        hl = make_head_linear_inputs(N, C, S, dtype, seed=2)
+        W = hl["W"].to(dev)
+        x = hl["x"].to(dev)
+        ms = _time(lambda: ops.head_linear_bwd_input(g, W, True), a.iters)
+        _line(f"head_linear {C}x{C} causal, input gradient", ms, nbytes=es * N * C * (tri + S * S), shape=shape, variant=a.variant)
+        ms = _time(lambda: ops.head_linear_bwd_weight(x, g, True), a.iters)
+        _line(f"head_linear {C}x{C} causal, weight gradient", ms, nbytes=2 * es * N * C * tri, shape=shape)
+        del x, g
     if a.which in ("qk", "pv", "all"):
         g = torch.Generator().manual_seed(3)
         q, k, v = (torch.randn(N, C, S, D, generator=g).to(dtype).to(dev) for _ in range(3))

@@ -7,7 +7,8 @@ chunk_start_ids) returning the (B,S,H,D) transpose view of a (B,H,S,D) tensor.
 
 `fused=True` (default) runs the whole forward through mta_fused_fwd.  `fused=False` runs the reference's
 seven steps one by one through the stand-alone entry points, which keeps every 16-bit rounding point of
-the reference.
+the reference.  `use_mask=True` runs the reference's explicit-mask path (None, boolean, additive, padding or
+(1,1,S,S) masks) stage by stage over full score planes.
 """
 import torch
 import torch.nn as nn
@@ -48,10 +49,10 @@ class MTAAttentionTriton(nn.Module):
 
     def forward(self, xq, xk, xv, mask=None, chunk_start_ids=None):
         assert chunk_start_ids is None, "MTAAttentionTriton does not support chunked attention"
-        if self.use_mask:
-            raise NotImplementedError("explicit masks (use_mask=True) are not implemented; the causal flag is")
         if self.training and self.dropout > 0.0:
             raise NotImplementedError("dropout on the attention weights is not implemented: use eval() or dropout=0")
+        if self.use_mask:
+            return self._forward_with_mask(xq, xk, xv, mask)
         if not self.causal:
             raise NotImplementedError("MTAAttentionTriton without a mask requires causal=True, as in the reference's benchmarks")
         if self.fused:
@@ -67,6 +68,50 @@ class MTAAttentionTriton(nn.Module):
         scores = self.wposm_triton(scores)
         output = ops.pv_fwd(scores, xv, causal=True)
         return output.transpose(1, 2)
+
+    def _forward_with_mask(self, xq, xk, xv, mask):
+        """The explicit-mask path of the reference (mta_attention_triton.py:63-92 with use_mask=True): full score
+        planes, the mask applied around the two convs and before the softmax exactly where the reference applies it.
+        The convs, head mixes, softmax and the two contractions are this library's kernels; the mask arithmetic
+        (masked_fill, add, where) is elementwise torch."""
+        mask = self._update_mask(mask=mask, bsz=xq.size(0), xq=xq, xk_size=xk.size(-2))
+        dead = mask == float("-inf")
+        head_dim = xq.size(-1)
+        scores = ops.qk_scores_fwd(xq, xk, head_dim ** -0.5, causal=False)
+        scores = self.mta_conv_triton(scores.masked_fill(dead, 0.0))
+        scores = self.wpsm_triton(scores)
+        scores = scores + mask
+        scores = ops.softmax_fwd(scores, causal=False)
+        scores = self.mta_conv_after_sm_triton(scores.masked_fill(dead, 0.0))
+        scores = torch.where(dead, torch.zeros((), dtype=scores.dtype, device=scores.device), scores)
+        scores = self.wposm_triton(scores)
+        output = ops.pv_fwd(scores, xv, causal=False)
+        return output.transpose(1, 2)
+
+    def _update_mask(self, mask, bsz: int, xq, xk_size: int):
+        """The reference's mask normalisation (mta_attention_triton.py:106-127): None -> the causal mask; bool -> 0 / -inf;
+        a (bsz, keys) padding mask -> broadcast over heads and queries with the causal part added; a (1,1,S,S) mask ->
+        repeated over batch and heads.  Returns a (B,H,S,S) tensor of 0 / -inf in the dtype of xq."""
+        if not isinstance(mask, torch.Tensor):
+            mask = torch.full((xq.size(-2), xk_size), float("-inf"), device=xq.device)
+            mask = torch.triu(mask, diagonal=1).type_as(xq)
+            mask = mask.repeat(bsz, self.n_heads, 1, 1)
+        else:
+            if mask.dtype == torch.bool:
+                mask = torch.where(mask, 0.0, float("-inf")).to(xq.dtype)
+            if mask.dtype != xq.dtype:
+                mask = mask.type(xq.dtype)
+            if len(mask.shape) == 2:
+                assert mask.size(0) == bsz
+                # (bsz, keys) -> (bsz, heads, queries, keys); the reference's repeat on the 2-D tensor is only
+                # shape-correct for bsz == 1, this is the same mask for that case and the evident intent otherwise
+                mask = mask[:, None, None, :].repeat(1, self.n_heads, xq.size(-2), 1)
+                mask_i, mask_j = torch.triu_indices(xq.size(-2), xk_size, offset=1)
+                mask[:, :, mask_i, mask_j] = float("-inf")
+            else:
+                if mask.size(0) == 1 and mask.size(1) == 1:
+                    mask = mask.repeat(bsz, self.n_heads, 1, 1)
+        return mask.to(xq.device)
 
     def forward_host(self, xq, xk, xv, out=None, chunk_batch: int = 0):
         """forward for HOST tensors (B,H,S,D), ideally page-locked: the library overlaps the transfers with the

@@ -195,3 +195,22 @@ def conv_attn_fwd(q, k, v, w, causal: bool = True, softmax_scale: Optional[float
     q = _f32(q)
     B, H, S, D = q.shape
     return np.stack([conv_attn_fwd_rows(q, k, v, w, b, 0, S, causal, softmax_scale, round_mode) for b in range(B)])
+
+
+def mta_fwd_masked(q, k, v, w1, W1, w2, W2, mask, causal: bool = True) -> np.ndarray:
+    """The explicit-mask forward (mta_attention_triton.py:63-92 with use_mask=True; with a mask that contains the causal
+    part it equals mta_attention_pytorch.py:56-83): mask (B,H,S,S) of 0 / -inf.  Full score planes in float64 / the C
+    primitives above; returns (B,H,S,D) float32.  Small sizes only."""
+    q, k, v, w1, W1, w2, W2 = map(_f32, (q, k, v, w1, W1, w2, W2))
+    mask = np.broadcast_to(_f32(mask), (q.shape[0], q.shape[1], q.shape[2], k.shape[2]))
+    dead = np.isneginf(mask)
+    scores = (np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), k.astype(np.float64)) / np.sqrt(q.shape[-1])).astype(np.float32)
+    scores = conv2d(np.where(dead, 0.0, scores).astype(np.float32), w1, causal)
+    scores = head_linear(scores, W1, causal, float("-inf"))
+    with np.errstate(invalid="ignore"):
+        scores = (scores + mask).astype(np.float32)
+    probs = softmax(scores, causal=False)
+    probs = conv2d(np.where(dead, 0.0, probs).astype(np.float32), w2, causal)
+    probs = np.where(dead, 0.0, probs).astype(np.float32)
+    probs = head_linear(probs, W2, causal, 0.0)
+    return np.einsum("bhqk,bhkd->bhqd", probs.astype(np.float64), v.astype(np.float64)).astype(np.float32)

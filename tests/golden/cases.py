@@ -67,6 +67,37 @@ HEAD_BWD_CASES = ["s1_h1", "s5_h3", "s63_h8", "s64_h16", "s65_h16", "s193_h5", "
 BACKWARD_GOLDEN = "golden_backward.npz"
 
 
+# Explicit-mask cases: name -> (MTA case name, mask kind).  Masks (make_mask below): "none" = the causal mask the
+# module builds itself; "padding" = a (1, S) boolean key mask (last keys padded out), batch 1; "documents" = a
+# (1,1,S,S) additive mask, causal inside concatenated documents and -inf across them.
+MASK_CASES = {
+    "tiny_none": ("tiny_f32", "none"),
+    "ragged_padding": ("ragged_f32", "padding"),
+    "ragged_documents": ("ragged_f32", "documents"),
+    "s130_bf16_documents": ("s130_6x11_bf16", "documents"),
+    "s257_documents": ("s257_6x11_f32", "documents"),
+}
+MASK_GOLDEN = "golden_masked.npz"
+
+
+def make_mask(kind: str, S: int, dtype):
+    """The mask argument of forward for a mask case (None, (1,S) bool, or (1,1,S,S) additive in `dtype`)."""
+    if kind == "none":
+        return None
+    if kind == "padding":
+        keep = torch.ones(1, S, dtype=torch.bool)
+        keep[:, S - max(1, S // 5):] = False
+        return keep
+    if kind == "documents":
+        bounds = [0, S // 3, (2 * S) // 3 + 1, S]
+        doc = torch.zeros(S, dtype=torch.long)
+        for i in range(3):
+            doc[bounds[i]:bounds[i + 1]] = i
+        ok = (doc[:, None] == doc[None, :]) & (torch.arange(S)[:, None] >= torch.arange(S)[None, :])
+        return torch.where(ok, 0.0, float("-inf")).to(dtype)[None, None]
+    raise ValueError(kind)
+
+
 def load_golden(path=None):
     """name -> float32 numpy array.  16-bit outputs are stored as bit patterns under 'name@bf16' / 'name@f16'."""
     import numpy as np

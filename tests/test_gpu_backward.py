@@ -53,10 +53,24 @@ def test_conv2d_backward_cases(name, golden_bwd):
         assert np.all(npf(dx)[..., iu[0], iu[1]] == 0.0)
 
 
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("S,R,Sk,causal", [(7, 3, 3, True), (96, 2, 7, True), (129, 6, 11, True), (200, 11, 15, True),
-                                           (70, 20, 21, True), (131, 4, 6, True), (66, 5, 9, False)])
-def test_conv2d_backward_shapes(S, R, Sk, causal, dtype):
+                                           (70, 20, 21, True), (131, 4, 6, True), (66, 5, 9, False), (264, 3, 3, True),
+                                           (512, 6, 11, True), (136, 1, 1, True), (320, 5, 9, False)])
+def test_conv2d_backward_shapes(S, R, Sk, causal, dtype, variant):
+    """variant 0: the tensor-core kernel where the shape allows it (16-bit, S % 8 == 0, odd key extent <= 17);
+    variant 1: CUDA cores."""
+    if variant == 1 and (dtype == torch.float32 or S % 8 or Sk % 2 == 0 or Sk > 17):
+        pytest.skip("same kernel as variant 0 for this shape")
+    _lib.set_variant("conv2d", variant)
+    try:
+        _conv2d_backward_shape(S, R, Sk, causal, dtype)
+    finally:
+        _lib.set_variant("conv2d", 0)
+
+
+def _conv2d_backward_shape(S, R, Sk, causal, dtype):
     inp = make_conv_inputs(2, 3, S, 16, R, Sk, dtype, seed=500 + S)
     w32 = inp["w"].float() + 1e-3 * torch.randn(3, R, Sk, generator=torch.Generator().manual_seed(S))
     g = make_upstream_grad((2, 3, S, S), dtype, 1500 + S)
@@ -98,8 +112,19 @@ def test_head_linear_backward_head_counts(C, dtype):
     inp = make_head_linear_inputs(2, C, S, dtype, seed=700 + C, mix_var=0.2)
     W32 = inp["W"].float() + 1e-3 * torch.randn(C, C, generator=torch.Generator().manual_seed(C))
     g = make_upstream_grad((2, C, S, S), dtype, 1700 + C)
-    dx = ops.head_linear_bwd_input(g.to(DEV), W32.to(DEV), True)
-    dW = ops.head_linear_bwd_weight(inp["x"].to(DEV), g.to(DEV), True)
+    xn, gn = inp["x"].clone(), g.clone()                 # garbage above the diagonal of x and dy must be ignored
+    iu = torch.triu_indices(S, S, 1)
+    xn[..., iu[0], iu[1]] = float("nan")
+    gn[..., iu[0], iu[1]] = float("nan")
+    dx = ops.head_linear_bwd_input(gn.to(DEV), W32.to(DEV), True)
+    dW = ops.head_linear_bwd_weight(xn.to(DEV), gn.to(DEV), True)
+    _lib.set_variant("head_linear", 1)                   # CUDA-core kernels
+    try:
+        dW1 = ops.head_linear_bwd_weight(xn.to(DEV), gn.to(DEV), True)
+    finally:
+        _lib.set_variant("head_linear", 0)
+    weight_grad_close(npf(dW1), orc.head_linear_bwd_weight(npf(inp["x"]), npf(g), True),
+                      orc.head_linear_bwd_weight(np.abs(npf(inp["x"])), np.abs(npf(g)), True), f"C={C} dW (CUDA cores)")
     _lib.device_status()
     input_grad_close(npf(dx), orc.head_linear_bwd_input(npf(g), npf(W32), True, ROUND[dtype]), dtype, f"C={C} dx")
     weight_grad_close(npf(dW), orc.head_linear_bwd_weight(npf(inp["x"]), npf(g), True),
