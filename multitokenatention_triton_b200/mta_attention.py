@@ -14,6 +14,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
+from .autograd_ops import CausalSoftmaxFunction, PVFunction, QKScoresFunction
 from .convolution_2d import Conv2dTriton
 from .linear_head import TritonLinearHead
 
@@ -55,18 +56,21 @@ class MTAAttentionTriton(nn.Module):
             return self._forward_with_mask(xq, xk, xv, mask)
         if not self.causal:
             raise NotImplementedError("MTAAttentionTriton without a mask requires causal=True, as in the reference's benchmarks")
-        if self.fused:
+        if self.fused and not (torch.is_grad_enabled() and any(
+                t.requires_grad for t in (xq, xk, xv, *self.parameters()))):
             out = ops.mta_fused_fwd(xq, xk, xv, self.mta_conv_triton.weight, self.wpsm_triton.weight,
                                     self.mta_conv_after_sm_triton.weight, self.wposm_triton.weight, causal=True)
             return out.transpose(1, 2)
+        # stage by stage; every stage is differentiable (the conv and the head mix through their backward kernels, the
+        # scores, the softmax and the product with V through autograd_ops), so this is the path a training step uses
         head_dim = xq.size(-1)
-        scores = ops.qk_scores_fwd(xq, xk, head_dim ** -0.5, causal=True)
+        scores = QKScoresFunction.apply(xq, xk, head_dim ** -0.5, True)
         scores = self.mta_conv_triton(scores)
         scores = self.wpsm_triton(scores)
-        scores = ops.softmax_fwd(scores, causal=True)
+        scores = CausalSoftmaxFunction.apply(scores, True)
         scores = self.mta_conv_after_sm_triton(scores)
         scores = self.wposm_triton(scores)
-        output = ops.pv_fwd(scores, xv, causal=True)
+        output = PVFunction.apply(scores, xv, True)
         return output.transpose(1, 2)
 
     def _forward_with_mask(self, xq, xk, xv, mask):

@@ -65,6 +65,8 @@ CONV_ATTN_CASES = {
 CONV_BWD_CASES = ["s1", "s5_3x3", "s63_3x5", "s64_6x11", "s65_6x11", "s130_5x7_noncausal", "s64_6x11_noncausal"]
 HEAD_BWD_CASES = ["s1_h1", "s5_h3", "s63_h8", "s64_h16", "s65_h16", "s193_h5", "s64_h16_noncausal"]
 BACKWARD_GOLDEN = "golden_backward.npz"
+# full-module gradients (dq, dk, dv and the four weights) of these MTA cases; upstream gradient seeded with seed + 2000
+MTA_BWD_CASES = ["tiny_f32", "ragged_f32", "c1b"]
 
 
 # Explicit-mask cases: name -> (MTA case name, mask kind).  Masks (make_mask below): "none" = the causal mask the

@@ -8,7 +8,8 @@ float32 on the seeded inputs of multitokenatention_triton_b200.synthetic (16-bit
 differentiated by autograd against the seeded upstream gradient, and the gradients are stored in golden_backward.npz.
 Where Triton's CPU interpreter can run them, the gradients of the reference's own autograd functions
 (Conv2dTritonFunction / TritonLinearHeadFunction, i.e. its backward kernels) are stored as well for the small float32
-cases; they pin the masks of the backward kernels.
+cases; they pin the masks of the backward kernels.  Full-module gradients (MTA_BWD_CASES): autograd through the reference's
+MTAAttention (mta_attention_pytorch.py) in float32.
 """
 import os
 import sys
@@ -77,12 +78,39 @@ def main(ref_path: str):
                 yt.backward(g.contiguous())
                 dx = xt.grad.float()
                 if causal:                                 # the reference leaves these entries uninitialised
-                    dx = dx * torch.tril(torch.ones(S, S))
+                    dx = torch.where(torch.tril(torch.ones(S, S, dtype=torch.bool)), dx, torch.zeros(()))
                 out[f"head_kernel_dx/{name}"] = dx.numpy()
                 out[f"head_kernel_dW/{name}"] = Wt.grad.float().numpy()
             except Exception as ex:
                 print("  reference Triton head-mix backward not stored for", name, "-", type(ex).__name__, str(ex)[:120])
         print("head backward", name)
+
+    import types
+    import mta_attention_pytorch as ref_mta
+    from make_golden import _patch_torch_tensor
+    from multitokenatention_triton_b200.synthetic import make_mta_inputs
+    from cases import MTA_BWD_CASES, MTA_CASES
+    _patch_torch_tensor()
+    for name in MTA_BWD_CASES:
+        wl = MTA_CASES[name]
+        inp = make_mta_inputs(wl)
+        cfg = types.SimpleNamespace(use_mta=True, query_kernel_size=wl.cq, key_kernel_size=wl.ck,
+                                    after_sm_query_kernel_size=wl.cq2, after_sm_key_kernel_size=wl.ck2,
+                                    pre_sm_linear_head=True, post_sm_linear_head=True, pad_key="both",
+                                    init_method="identity", dim=wl.H * wl.D)
+        m = ref_mta.MTAAttention(wl.H, cfg, dropout=0.0).eval().float()
+        with torch.no_grad():
+            m.mta_kernel.copy_(inp["w1"].float().unsqueeze(1))
+            m.wpsm.weight.copy_(inp["W1"].float())
+            m.mta_kernel_after_sm.copy_(inp["w2"].float().unsqueeze(1))
+            m.wposm.weight.copy_(inp["W2"].float())
+        q, k, v = (inp[x].float().clone().requires_grad_() for x in ("q", "k", "v"))
+        g = make_upstream_grad((wl.B, wl.S, wl.H, wl.D), wl.dtype, wl.seed + 2000).float()
+        m(q, k, v, None, None).backward(g)
+        for key, t in (("dq", q.grad), ("dk", k.grad), ("dv", v.grad), ("dw1", m.mta_kernel.grad.squeeze(1)),
+                       ("dW1", m.wpsm.weight.grad), ("dw2", m.mta_kernel_after_sm.grad.squeeze(1)), ("dW2", m.wposm.weight.grad)):
+            out[f"mta_{key}/{name}"] = t.detach().numpy().copy()
+        print("mta backward", name)
 
     path = os.path.join(HERE, BACKWARD_GOLDEN)
     np.savez_compressed(path, **out)

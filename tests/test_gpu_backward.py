@@ -188,3 +188,36 @@ def test_backward_at_score_plane_size():
     assert abs(lhs - float((dp.double() * torch.tril(p).double()).sum())) <= 4e-3 * scale
     assert abs(lhs - float((dW.double() * W.double()).sum())) <= 4e-3 * scale
     assert torch.equal(ops.head_linear_bwd_weight(p, g, True), dW)
+
+
+@pytest.mark.parametrize("name", ["tiny_f32", "ragged_f32", "c1b"])
+def test_module_gradients_against_the_reference(name, golden_bwd):
+    """loss.backward() through MTAAttentionTriton (the stage-by-stage path a training step takes) against autograd
+    through the reference's MTAAttention: gradients of q, k, v and of the four weights."""
+    import types
+    from cases import MTA_CASES
+    from multitokenatention_triton_b200 import MTAAttentionTriton
+    from multitokenatention_triton_b200.synthetic import make_mta_inputs
+    wl = MTA_CASES[name]
+    inp = make_mta_inputs(wl)
+    cfg = types.SimpleNamespace(use_mta=True, query_kernel_size=wl.cq, key_kernel_size=wl.ck,
+                                after_sm_query_kernel_size=wl.cq2, after_sm_key_kernel_size=wl.ck2,
+                                pre_sm_linear_head=True, post_sm_linear_head=True, pad_key="both", init_method="identity",
+                                dim=wl.H * wl.D)
+    m = MTAAttentionTriton(wl.H, cfg, dropout=0.0, causal=True).to(DEV).to(wl.dtype).eval()
+    with torch.no_grad():
+        m.mta_conv_triton.weight.copy_(inp["w1"])
+        m.wpsm_triton.weight.copy_(inp["W1"])
+        m.mta_conv_after_sm_triton.weight.copy_(inp["w2"])
+        m.wposm_triton.weight.copy_(inp["W2"])
+    q, k, v = (inp[x].to(DEV).requires_grad_() for x in ("q", "k", "v"))
+    g = make_upstream_grad((wl.B, wl.S, wl.H, wl.D), wl.dtype, wl.seed + 2000).to(DEV)
+    m(q, k, v, None, None).backward(g)
+    _lib.device_status()
+    got = {"dq": q.grad, "dk": k.grad, "dv": v.grad, "dw1": m.mta_conv_triton.weight.grad, "dW1": m.wpsm_triton.weight.grad,
+           "dw2": m.mta_conv_after_sm_triton.weight.grad, "dW2": m.wposm_triton.weight.grad}
+    for key, t in got.items():
+        ref = golden_bwd[f"mta_{key}/{name}"]
+        err = float(np.max(np.abs(npf(t) - ref)))
+        scale = max(1.0, float(np.max(np.abs(ref))))
+        assert err <= 1e-3 * scale, f"{name} {key}: max abs {err:.3e} against scale {scale:.3e}"
