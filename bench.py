@@ -332,8 +332,8 @@ def main():
         barrier()
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        h2d = sum(host[k].numel() * host[k].element_size() for k in host)
-        d2h = out_host.numel() * out_host.element_size()
+        h2d = world * sum(host[k].numel() * host[k].element_size() for k in host)      # whole job, like the value
+        d2h = world * out_host.numel() * out_host.element_size()
         e2e = {"value": tokens / (float(t.item()) / n_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": n_e2e,
                "path": "MTAAttentionTriton.forward_host -> mta_fused_fwd_host: batch chunks on three streams, host clock around the blocking call"}
