@@ -209,6 +209,9 @@ def stage_table(wl: MTAWorkload, samples, peaks):
         if name in ("qk_scores", "pv"):
             nbytes = float(es) * lower + 2 * qkv_bytes        # the score triangle written (read) + two operands
             row.update(bound="hbm", tflops=2.0 * wl.D * lower / (ms * 1e-3) / 1e12)
+        elif name == "qk_scores+conv1":
+            nbytes = float(es) * lower + 2 * qkv_bytes        # Q and K read, the conv's triangle written; no score plane
+            row.update(bound="hbm", tflops=(2.0 * wl.D + 2.0 * wl.cq * wl.ck) * lower / (ms * 1e-3) / 1e12)
         else:
             nbytes = 2.0 * es * lower
             row.update(bound="hbm")

@@ -191,9 +191,9 @@ void mta_reset_launch_count(void);
 
 /* Selects implementation variants for A/B measurement: key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core;
  * key "conv2d" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core, 3 tcgen05 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core,
- * 2 tcgen05 tensor-core; key "fused" (mta_fused_fwd) -> 0 auto (one kernel per stage, the first head mix and the
- * softmax as one kernel), 1 strictly one kernel per stage, 2 fused conv + head-mix stages with the softmax folded in (16-bit
- * dtypes, H <= 16).  Returns 0, or 1 for an unknown key/value. */
+ * 2 tcgen05 tensor-core; key "fused" (mta_fused_fwd) -> 0 auto (Q K^T inside the first conv's kernel, the first
+ * head mix and the softmax as one kernel), 1 strictly one kernel per stage, 2 fused conv + head-mix stages with the softmax
+ * folded in (16-bit dtypes, H <= 16), 3 Q K^T and the first conv as two kernels, head mix + softmax as one.  Returns 0, or 1 for an unknown key/value. */
 int mta_set_variant(const char* key, int value);
 
 #ifdef __cplusplus

@@ -125,8 +125,17 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     const int round16 = dtype != MTA_F32;
     int rc;
     g_trace_n = 0;
+    // Default for 16-bit dtypes: the scores are computed inside the first conv's kernel and never stored
+    // (mta_set_variant("fused", 3) keeps the two kernels apart, as do the "gemm" and "conv2d" variants).
+    const bool qk_in_conv = variant("fused") == 0 && variant("gemm") == 0 && variant("conv2d") == 0 && planes <= 65535 &&
+                            qk_conv_supported(q, k, bufB, pv, S, D, cq, ck, causal, dtype, w_dtype);
+    if (qk_in_conv) {
+        if ((rc = trace_mark("qk_scores+conv1", st))) return rc;
+        if ((rc = qk_conv_launch(q, k, w1, w_dtype, bufB, pv, B, H, S, D, cq, ck, scale, pl.rb, pl.r1, dtype, st))) return rc;
+    } else {
     if ((rc = trace_mark("qk_scores", st))) return rc;
     if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, scale, round16, causal, pl.ra, pl.r1, dtype, st))) return rc;
+    }
     // mta_set_variant("fused", 2): two fused "conv + head mix" launches with the softmax folded into them.  Measured at
     // B8 H16 S4096: 12.1 ms per forward against 7.8 ms for the stage-by-stage pipeline below - both the conv and the
     // mix run on the legacy mma.sync pipes, which a single CTA keeps less busy than several independent kernels do -
@@ -148,8 +157,10 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
         if ((rc = pv_launch(bufA, pv, nrows, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st))) return rc;
         return trace_end(st);
     }
-    if ((rc = trace_mark("conv1", st))) return rc;
-    if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
+    if (!qk_in_conv) {
+        if ((rc = trace_mark("conv1", st))) return rc;
+        if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
+    }
     // the first head mix and the softmax run as one kernel where it applies (mta_set_variant("fused", 1) keeps them apart)
     if (variant("fused") != 1 && head_mix_softmax_supported(bufB, pv, bufA, pv, H, S, causal, dtype)) {
         if ((rc = trace_mark("head_mix1+softmax", st))) return rc;

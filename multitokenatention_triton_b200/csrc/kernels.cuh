@@ -90,6 +90,12 @@ int pv_tc05_launch(const void* p, PlaneView pview, long p_rows_stored, const voi
 int qk_persistent_launch(const void* a, const void* b, void* c, PlaneView cv, int B, int H, int S, int D, int NI, float scale,
                          int round_scale, int causal, int mode, int band_cq, int band_pw, int row_begin, int row_end, int dtype,
                          cudaStream_t st);
+// Scaled scores Q K^T and the causal conv of them in one kernel (qk_conv_tc05.cu): y = conv(round(round(Q K^T) scale)),
+// rows [row_begin,row_end); the score planes never reach memory.  16-bit dtypes, D in {64,128}, odd key extent <= 17.
+bool qk_conv_supported(const void* q, const void* k, const void* y, PlaneView yv, int S, int D, int R, int KS, int causal, int dtype,
+                       int w_dtype);
+int qk_conv_launch(const void* q, const void* k, const void* w, int w_dtype, void* y, PlaneView yv, int B, int H, int S, int D,
+                   int R, int KS, float scale, int row_begin, int row_end, int dtype, cudaStream_t st);
 // Reads and clears the flag raised by a device-side bounded wait that gave up (synchronises `st`).
 int device_wait_status(cudaStream_t st, int* timed_out);
 

@@ -306,6 +306,28 @@ def test_mta_forward_fused_stages_agree_with_stage_by_stage(name):
     assert_parity(npf(fused), orc.mta_fwd(*a, True, orc.ROUND_NONE), wl.dtype, f"{name} fused stages vs oracle")
 
 
+@pytest.mark.parametrize("name", ["s130_6x11_bf16", "s128_11x15_bf16", "s192_h32_f16"])
+def test_scores_computed_inside_the_first_conv_change_no_bit(name):
+    """Default forward (Q K^T computed inside the first conv's kernel, never stored) against the forward with the two
+    kernels apart: the conv reads the same rounded scores in the same order, so the outputs are identical - also for a
+    row range, whose tiles start at other rows."""
+    wl = MTA_CASES[name]
+    inp = make_mta_inputs(wl)
+    args = [inp[k].to(DEV) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    folded = ops.mta_fused_fwd(*args, True)
+    part = torch.zeros_like(folded)
+    ops.mta_fused_fwd(*args, True, rows=(9, wl.S - 2), out=part)
+    _lib.device_status()
+    try:
+        _lib.set_variant("fused", 3)
+        apart = ops.mta_fused_fwd(*args, True)
+    finally:
+        _lib.set_variant("fused", 0)
+    _lib.device_status()
+    assert torch.equal(folded, apart)
+    assert torch.equal(part[:, :, 9:wl.S - 2], folded[:, :, 9:wl.S - 2])
+
+
 def test_stage_trace_reports_every_kernel_of_the_forward():
     wl = MTA_CASES["s128_11x15_bf16"]
     inp = make_mta_inputs(wl)
@@ -314,8 +336,11 @@ def test_stage_trace_reports_every_kernel_of_the_forward():
     try:
         ops.mta_fused_fwd(*args, True)
         got = _lib.stage_times_ms()
-        assert [n for n, _ in got] == ["qk_scores", "conv1", "head_mix1+softmax", "conv2", "head_mix2", "pv"]
+        assert [n for n, _ in got] == ["qk_scores+conv1", "head_mix1+softmax", "conv2", "head_mix2", "pv"]
         assert all(0.0 < ms < 100.0 for _, ms in got)
+        _lib.set_variant("fused", 3)
+        ops.mta_fused_fwd(*args, True)
+        assert [n for n, _ in _lib.stage_times_ms()] == ["qk_scores", "conv1", "head_mix1+softmax", "conv2", "head_mix2", "pv"]
         _lib.set_variant("fused", 1)
         ops.mta_fused_fwd(*args, True)
         assert [n for n, _ in _lib.stage_times_ms()] == ["qk_scores", "conv1", "head_mix1", "softmax", "conv2", "head_mix2", "pv"]
