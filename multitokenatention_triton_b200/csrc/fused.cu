@@ -207,8 +207,14 @@ int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w
     const PlaneView pv{(long)S * S, 0, S};
     const long planes = (long)B * H;
     int rc;
-    if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, 1.0f, 0, causal, 0, S, dtype, st))) return rc;
-    if ((rc = conv2d_launch(bufA, pv, S, w, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, 0, S, !causal, dtype, st))) return rc;
+    // 16-bit dtypes: the raw scores are computed inside the conv's kernel (scale 1: the conv attention scales after its conv)
+    if (variant("fused") == 0 && variant("gemm") == 0 && variant("conv2d") == 0 && planes <= 65535 &&
+        qk_conv_supported(q, k, bufB, pv, S, D, cq, ck, causal, dtype, w_dtype)) {
+        if ((rc = qk_conv_launch(q, k, w, w_dtype, bufB, pv, B, H, S, D, cq, ck, 1.0f, 0, S, dtype, st))) return rc;
+    } else {
+        if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, 1.0f, 0, causal, 0, S, dtype, st))) return rc;
+        if ((rc = conv2d_launch(bufA, pv, S, w, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, 0, S, !causal, dtype, st))) return rc;
+    }
     if ((rc = softmax_launch(bufB, pv, bufB, pv, planes, S, S, causal, 0, S, false, scale, dtype, st))) return rc;
     return pv_launch(bufB, pv, S, v, o, B, H, S, D, causal, 0, S, dtype, st);
 }
