@@ -185,7 +185,8 @@ def event_time_ms(fn, iters: int) -> float:
 # captures of smaller cases of the same kernels (the summaries under profiles/ give the commands); a launch's traffic
 # grows in proportion to the triangle it processes.
 NCU_DRAM_BYTES_PER_LOWER_ELEMENT = {       # profiles/mta_forward_kernels_b1_s4096.md (B1 H16 S4096: 134.25 M scores)
-    "qk_scores": 2.01, "conv1": 4.07, "head_mix1+softmax": 3.63, "conv2": 4.00, "head_mix2": 3.73, "pv": 2.28,
+    "qk_scores+conv1": 2.03, "qk_scores": 2.01, "conv1": 4.07, "head_mix1+softmax": 3.62, "conv2": 3.99, "head_mix2": 3.71,
+    "pv": 2.28,
 }
 
 
