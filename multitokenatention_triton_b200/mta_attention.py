@@ -12,6 +12,7 @@ the reference.  `use_mask=True` runs the reference's explicit-mask path (None, b
 """
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from . import ops
 from .autograd_ops import CausalSoftmaxFunction, PVFunction, QKScoresFunction
@@ -50,13 +51,12 @@ class MTAAttentionTriton(nn.Module):
 
     def forward(self, xq, xk, xv, mask=None, chunk_start_ids=None):
         assert chunk_start_ids is None, "MTAAttentionTriton does not support chunked attention"
-        if self.training and self.dropout > 0.0:
-            raise NotImplementedError("dropout on the attention weights is not implemented: use eval() or dropout=0")
         if self.use_mask:
             return self._forward_with_mask(xq, xk, xv, mask)
         if not self.causal:
             raise NotImplementedError("MTAAttentionTriton without a mask requires causal=True, as in the reference's benchmarks")
-        if self.fused and not (torch.is_grad_enabled() and any(
+        dropping = self.training and self.dropout > 0.0
+        if self.fused and not dropping and not (torch.is_grad_enabled() and any(
                 t.requires_grad for t in (xq, xk, xv, *self.parameters()))):
             out = ops.mta_fused_fwd(xq, xk, xv, self.mta_conv_triton.weight, self.wpsm_triton.weight,
                                     self.mta_conv_after_sm_triton.weight, self.wposm_triton.weight, causal=True)
@@ -70,6 +70,7 @@ class MTAAttentionTriton(nn.Module):
         scores = CausalSoftmaxFunction.apply(scores, True)
         scores = self.mta_conv_after_sm_triton(scores)
         scores = self.wposm_triton(scores)
+        scores = F.dropout(scores, p=self.dropout, training=self.training)      # mta_attention_triton.py:87
         output = PVFunction.apply(scores, xv, True)
         return output.transpose(1, 2)
 
@@ -89,6 +90,7 @@ class MTAAttentionTriton(nn.Module):
         scores = self.mta_conv_after_sm_triton(scores.masked_fill(dead, 0.0))
         scores = torch.where(dead, torch.zeros((), dtype=scores.dtype, device=scores.device), scores)
         scores = self.wposm_triton(scores)
+        scores = F.dropout(scores, p=self.dropout, training=self.training)
         output = ops.pv_fwd(scores, xv, causal=False)
         return output.transpose(1, 2)
 

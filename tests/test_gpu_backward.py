@@ -221,3 +221,37 @@ def test_module_gradients_against_the_reference(name, golden_bwd):
         err = float(np.max(np.abs(npf(t) - ref)))
         scale = max(1.0, float(np.max(np.abs(ref))))
         assert err <= 1e-3 * scale, f"{name} {key}: max abs {err:.3e} against scale {scale:.3e}"
+
+
+def test_dropout_in_training_mode():
+    """dropout > 0 in training mode is applied to the attention weights before the product with V, as the reference does
+    (mta_attention_triton.py:87): p = 0 in training mode equals eval, p > 0 is unbiased."""
+    import types
+    from cases import MTA_CASES
+    from multitokenatention_triton_b200 import MTAAttentionTriton
+    from multitokenatention_triton_b200.synthetic import make_mta_inputs
+    wl = MTA_CASES["c1"]
+    inp = make_mta_inputs(wl)
+    cfg = types.SimpleNamespace(use_mta=True, query_kernel_size=wl.cq, key_kernel_size=wl.ck,
+                                after_sm_query_kernel_size=wl.cq2, after_sm_key_kernel_size=wl.ck2,
+                                pre_sm_linear_head=True, post_sm_linear_head=True, pad_key="both", init_method="identity",
+                                dim=wl.H * wl.D)
+    q, k, v = (inp[x].to(DEV) for x in ("q", "k", "v"))
+    outs = {}
+    for p in (0.0, 0.5):
+        m = MTAAttentionTriton(wl.H, cfg, dropout=p, causal=True).to(DEV)
+        with torch.no_grad():
+            m.mta_conv_triton.weight.copy_(inp["w1"])
+            m.wpsm_triton.weight.copy_(inp["W1"])
+            m.mta_conv_after_sm_triton.weight.copy_(inp["w2"])
+            m.wposm_triton.weight.copy_(inp["W2"])
+            ref = m.eval()(q, k, v, None, None)
+            m.train()
+            torch.manual_seed(0)
+            outs[p] = torch.stack([m(q, k, v, None, None) for _ in range(64 if p else 1)]).mean(0)
+        if p == 0.0:
+            assert torch.allclose(outs[p], ref, atol=1e-5)
+        else:
+            assert not torch.allclose(outs[p], ref, atol=1e-3)
+            assert float((outs[p] - ref).abs().mean()) < 0.25 * float(ref.abs().mean())
+    _lib.device_status()
