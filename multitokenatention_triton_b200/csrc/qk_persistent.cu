@@ -5,7 +5,7 @@
 //   NI = 1, B_0 = K          plain scaled scores Q K^T * scale (mta_attention_triton.py:68-71)
 //   NI = cq, B_i = Kt_i      the causal conv of the scores for tiles that lie wholly below the causal band, through
 //                            the bilinear identity conv(Q K^T)[q,k] = sum_i Q[q-(cq-1)+i] . Kt_i[k] with
-//                            Kt_i[k] = scale * sum_j w[i][j] K[k + j - pad_w]   (see kt_prepare.cu)
+//                            Kt_i[k] = scale * sum_j w[i][j] K[k + j - pad_w]   (prepared by the caller)
 //
 // One CTA per SM walks a contiguous range of tiles.  Warp 0 issues the TMA loads (A rows shifted per term, both
 // operands in the 128-byte-swizzled K-major layout, out-of-range rows read as zero) into a ring of stages; warp 1
