@@ -1,6 +1,6 @@
 """Micro-benchmarks of the stand-alone kernels on the configurations their roofline targets are quoted on.
 
-    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|mix_softmax|qk|pv|backward|all] [--variant V]
+    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|mix_softmax|qk|pv|backward|conv_attn|all] [--variant V]
                                                         [--batch N] [--seq S] [--iters K]
 
   conv2d       causal depthwise conv 6x11 on a (B=4, H=16, S=2048, S) bf16 score plane
@@ -63,7 +63,7 @@ def _line(name, ms, nbytes=None, flops=None, **extra):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "mix_softmax", "qk", "pv", "backward", "all"])
+    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "mix_softmax", "qk", "pv", "backward", "conv_attn", "all"])
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--heads", type=int, default=16)
@@ -148,6 +148,14 @@ def main():
             ms = _time(lambda: ops.pv_fwd(s, v, True), a.iters)
             _line("pv causal", ms, flops=2.0 * D * N * C * tri, shape=shape + f" D{D}", variant=a.variant,
                   read_gbs=es * N * C * tri / ms / 1e6)
+    if a.which in ("conv_attn", "all"):
+        # the fused conv attention softmax(scale * conv(Q K^T)) V (TritonConvAttention): three launches
+        g = torch.Generator().manual_seed(5)
+        q, k, v = (torch.randn(N, C, S, D, generator=g).to(dtype).to(dev) for _ in range(3))
+        w = (torch.randn(C, 6, 11, generator=g) / 66 ** 0.5).to(dtype).to(dev)
+        ms = _time(lambda: ops.conv_attn_fwd(q, k, v, w, True, D ** -0.5), a.iters)
+        _line("conv attention 6x11 causal", ms, flops=(4.0 * D + 2.0 * 66) * N * C * tri, shape=shape + f" D{D}",
+              tokens_per_s=N * S / (ms * 1e-3))
     _lib.device_status()
 
 
