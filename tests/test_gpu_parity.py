@@ -14,7 +14,7 @@ import torch
 from cases import CONV_ATTN_CASES, CONV_CASES, HEAD_CASES, MTA_CASES
 from multitokenatention_triton_b200 import (Conv2dTriton, MTAAttentionTriton, TritonConvAttention, TritonLinearHead,
                                             _lib, ops)
-from multitokenatention_triton_b200.synthetic import make_conv_inputs, make_head_linear_inputs, make_mta_inputs
+from multitokenatention_triton_b200.synthetic import MTAWorkload, make_conv_inputs, make_head_linear_inputs, make_mta_inputs
 from oracle import mta_oracle as orc
 from util import ROUND, assert_parity, max_abs, npf, rel_fro, rel_max
 
@@ -326,6 +326,20 @@ def test_scores_computed_inside_the_first_conv_change_no_bit(name):
     _lib.device_status()
     assert torch.equal(folded, apart)
     assert torch.equal(part[:, :, 9:wl.S - 2], folded[:, :, 9:wl.S - 2])
+
+
+@pytest.mark.parametrize("H,S,D,cq,ck,dtype", [(128, 72, 32, 3, 5, torch.float16), (4, 160, 64, 77, 77, torch.float16),
+                                              (64, 96, 64, 6, 11, torch.bfloat16), (2, 200, 128, 21, 21, torch.float32)])
+def test_mta_forward_published_shape_limits(H, S, D, cq, ck, dtype):
+    """Shapes at the edges of what the reference publishes numbers for (up to 128 heads, conv kernels up to 77 x 77,
+    fp16): they run through the general kernels and must match the oracle like every other case."""
+    wl = MTAWorkload("limits", 1, H, S, D, cq, ck, 3, 3, dtype, seed=70 + H, random_post_conv=True)
+    inp = make_mta_inputs(wl)
+    args = [inp[k].to(DEV) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    out = ops.mta_fused_fwd(*args, True)
+    _lib.device_status()
+    a = [npf(inp[k]) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    assert_parity(npf(out), orc.mta_fwd(*a, True, orc.ROUND_NONE), dtype, f"H{H} S{S} {cq}x{ck}")
 
 
 def test_stage_trace_reports_every_kernel_of_the_forward():
