@@ -111,8 +111,9 @@ def cpu_port_tokens_per_s(wl: MTAWorkload, budget_s: float, threads: int = 0):
     of batch element 0 centred on S/2, where a row's cost equals the workload's mean cost per token.
     The block is grown until it needs about `budget_s` seconds.  Returns (tokens/s, cores, description)."""
     from oracle import mta_oracle as orc
-    if threads:
-        orc.set_threads(threads)
+    if not threads:      # all the cores this process may run on, whatever OMP_NUM_THREADS a launcher exported
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    orc.set_threads(threads)
     cores = orc.num_threads()
     if wl not in _CPU_INPUTS:
         inp = make_mta_inputs(wl, batch_slice=slice(0, 1))
@@ -149,8 +150,11 @@ def reference_arm(args, wl: MTAWorkload, rank: int):
         return
     per_step_budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
     vals, cores, desc = [], 1, ""
+    # every host core this process may use: torchrun exports OMP_NUM_THREADS=1 to its workers, and the other ranks of
+    # this arm exit without work, so the cores are free
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     for i in range(args.warmup + args.steps):
-        v, cores, desc = cpu_port_tokens_per_s(wl, per_step_budget)
+        v, cores, desc = cpu_port_tokens_per_s(wl, per_step_budget, threads=threads)
         if i >= args.warmup:
             vals.append(v)
     value = statistics.mean(vals) if vals else 0.0
