@@ -264,14 +264,17 @@ qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 // diagonal P tile that lies above the diagonal, then issues the MMAs; warps 2..5: epilogue.
 constexpr int PV_STAGES = 3;
 constexpr int PV_THREADS = 192;
+constexpr int PV_KEYS = 64;               // keys per pipeline stage: 32 KB stages, so two CTAs fit on an SM and one CTA's
+                                          // start-up and epilogue overlap the other's steady state
+constexpr int PV_VBOX_BYTES = PV_KEYS * 128;   // one box of the V tile: 64 keys x 64 elements
 
 template <typename T, int D>
 __global__ void __launch_bounds__(PV_THREADS)
 pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ CUtensorMap mv, T* __restrict__ o,
                int p_row0, int S, int causal, int row_begin, int row_end, int* err_flag) {
     constexpr int NBOX_V = D / 64;
-    constexpr int P_BYTES = 2 * BOX_BYTES;                 // 128 q x 128 k
-    constexpr int V_BYTES = NBOX_V * BOX_BYTES;            // 128 k x D
+    constexpr int P_BYTES = BOX_BYTES;                     // 128 q x 64 k
+    constexpr int V_BYTES = NBOX_V * PV_VBOX_BYTES;        // 64 k x D
     constexpr int STAGE_BYTES = P_BYTES + V_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_1024(smem_raw);
@@ -288,7 +291,8 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
     const int bh = (int)blockIdx.y;
     const int q0 = row_begin + tq * TILE;
     const int q_end = min(q0 + TILE, row_end);
-    const int nk = key_tiles_for(tq, row_begin, row_end, S, causal);
+    // 64-key steps that hold a key <= the tile's last query
+    const int nk = causal ? min((q_end + PV_KEYS - 1) / PV_KEYS, (S + PV_KEYS - 1) / PV_KEYS) : (S + PV_KEYS - 1) / PV_KEYS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (warp == 0) {
@@ -318,10 +322,9 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
                 uint8_t* sp = smem + st * STAGE_BYTES;
                 uint8_t* sv = sp + P_BYTES;
                 mbar_expect_tx(&full_bar[st], STAGE_BYTES);
-                tma_load_3d(sp, &mp, &full_bar[st], kt * TILE, q0 - p_row0, bh);
-                tma_load_3d(sp + BOX_BYTES, &mp, &full_bar[st], kt * TILE + 64, q0 - p_row0, bh);
+                tma_load_3d(sp, &mp, &full_bar[st], kt * PV_KEYS, q0 - p_row0, bh);
 #pragma unroll
-                for (int j = 0; j < NBOX_V; ++j) tma_load_3d(sv + j * BOX_BYTES, &mv, &full_bar[st], j * 64, kt * TILE, bh);
+                for (int j = 0; j < NBOX_V; ++j) tma_load_3d(sv + j * PV_VBOX_BYTES, &mv, &full_bar[st], j * 64, kt * PV_KEYS, bh);
             }
         }
     } else if (warp == 1) {
@@ -331,15 +334,15 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
             uint8_t* sp = smem + st * STAGE_BYTES;
             uint8_t* sv = sp + P_BYTES;
             mbar_wait(&full_bar[st], use & 1, err_flag);
-            const int k0 = kt * TILE;
-            if (causal && k0 + TILE - 1 > q0) {
+            const int k0 = kt * PV_KEYS;
+            if (causal && k0 + PV_KEYS - 1 > q0) {
                 // Keys above the diagonal must contribute nothing, whatever the buffer holds there.
-                // Element (row r, key c) of the swizzled tile: box c/64, byte r*128 + (((c%64)/8) ^ (r%8))*16 + (c%8)*2.
-                for (int idx = lane; idx < TILE * 16; idx += 32) {
-                    const int r = idx >> 4, ch = idx & 15;             // 16-byte chunk ch covers keys 8ch..8ch+7
+                // Element (row r, key c) of the swizzled tile: byte r*128 + ((c/8) ^ (r%8))*16 + (c%8)*2.
+                for (int idx = lane; idx < TILE * 8; idx += 32) {
+                    const int r = idx >> 3, ch = idx & 7;              // 16-byte chunk ch covers keys 8ch..8ch+7
                     const int qrow = q0 + r, kfirst = k0 + ch * 8;
                     if (kfirst + 7 <= qrow) continue;
-                    uint8_t* chunk = sp + (ch >> 3) * BOX_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+                    uint8_t* chunk = sp + r * 128 + ((ch ^ (r & 7)) << 4);
                     if (kfirst > qrow) {
                         *reinterpret_cast<uint4*>(chunk) = make_uint4(0u, 0u, 0u, 0u);
                     } else {
@@ -354,9 +357,9 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
             fence_after_sync();
             if (lane == 0) {
 #pragma unroll
-                for (int kk = 0; kk < TILE / 16; ++kk) {
-                    const uint64_t da = smem_desc_sw128(smem_u32(sp) + (kk / 4) * BOX_BYTES + (kk % 4) * 32, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(smem_u32(sv) + kk * 16 * 128, BOX_BYTES, 1024);
+                for (int kk = 0; kk < PV_KEYS / 16; ++kk) {
+                    const uint64_t da = smem_desc_sw128(smem_u32(sp) + kk * 32, 16, 1024);
+                    const uint64_t db = smem_desc_sw128(smem_u32(sv) + kk * 16 * 128, PV_VBOX_BYTES, 1024);
                     mma_f16_ss(tmem, da, db, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
                 }
                 mma_commit(&empty_bar[st]);
@@ -426,11 +429,11 @@ int launch_pv(const void* p, PlaneView pview, const void* v, void* o, int B, int
     CUtensorMap mp, mv;
     int rc;
     if ((rc = make_tensor_map_3d(&mp, p, (uint64_t)B * H, (uint64_t)p_rows_stored, S, S, (uint64_t)pview.plane_stride, 64, TILE, true))) return rc;
-    if ((rc = make_tensor_map_3d(&mv, v, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
+    if ((rc = make_tensor_map_3d(&mv, v, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, PV_KEYS, true))) return rc;
     int* flag = nullptr;
     if ((rc = wait_flag_ptr(&flag))) return rc;
     const int n_qt = (row_end - row_begin + TILE - 1) / TILE;
-    const size_t smem = (size_t)PV_STAGES * (2 * BOX_BYTES + (D / 64) * BOX_BYTES) + 1024;
+    const size_t smem = (size_t)PV_STAGES * (BOX_BYTES + (D / 64) * PV_VBOX_BYTES) + 1024;
     MTA_CUDA_OK(cudaFuncSetAttribute(pv_tc05_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)n_qt, (unsigned)(B * H));
     pv_tc05_kernel<T, D><<<grid, PV_THREADS, smem, st>>>(mp, mv, static_cast<T*>(o), pview.row0, S, causal, row_begin,
