@@ -7,6 +7,7 @@ mta_conv2d_bwd_input / mta_conv2d_bwd_weight.
 """
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 from torch.autograd import Function
 
 from . import ops
@@ -33,8 +34,16 @@ class Conv2dTritonFunction(Function):
 
 
 class Conv2dTriton(nn.Module):
-    def __init__(self, channels, kernel_size, causal=False):
+    """`pad_key` places the key window as MTAAttention._mta_convolution does (mta_attention_pytorch.py:91-103): "both"
+    (the reference's Triton kernel, window centred on the key), "left" (keys k-(S-1)..k) or "right" (keys k..k+S-1).
+    "left" / "right" run the same kernels on the (C,R,2S-1) kernel that carries the S taps on one side of its centre
+    and zeros on the other - the same sums, term by term - and the weight gradient comes back through that padding."""
+
+    def __init__(self, channels, kernel_size, causal=False, pad_key="both"):
         super().__init__()
+        if pad_key not in ("both", "left", "right"):
+            raise ValueError(f"pad_key must be 'both', 'left' or 'right', not {pad_key!r}")
+        self.pad_key = pad_key
         self.channels = channels
         self.kernel_size = kernel_size if isinstance(kernel_size, tuple) else (kernel_size, kernel_size)
         self.causal = causal
@@ -47,5 +56,14 @@ class Conv2dTriton(nn.Module):
             self.weight.zero_()
             self.weight[:, self.kernel_size[0] // 2, self.kernel_size[1] // 2] = 1.0
 
+    def effective_weight(self):
+        """The kernel the CUDA entry points take: the weight itself for pad_key "both", else its zero-extended form."""
+        S = self.kernel_size[1]
+        if self.pad_key == "left":
+            return F.pad(self.weight, (0, S - 1))
+        if self.pad_key == "right":
+            return F.pad(self.weight, (S - 1, 0))
+        return self.weight
+
     def forward(self, x):
-        return Conv2dTritonFunction.apply(x, self.weight, self.causal)
+        return Conv2dTritonFunction.apply(x, self.effective_weight(), self.causal)

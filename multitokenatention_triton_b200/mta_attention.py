@@ -40,13 +40,18 @@ class MTAAttentionTriton(nn.Module):
         self.use_mask = use_mask
         self.fused = fused
 
-        self.mta_conv_triton = Conv2dTriton(n_heads, kernel_size=(mta.query_kernel_size, mta.key_kernel_size), causal=causal)
+        # the reference's Triton module only takes pad_key "both" (mta_attention_triton.py:171); "left" and "right" are
+        # those of its PyTorch module (mta_attention_pytorch.py:91-98)
+        pad_key = getattr(mta, "pad_key", "both")
+        self.mta_conv_triton = Conv2dTriton(n_heads, kernel_size=(mta.query_kernel_size, mta.key_kernel_size), causal=causal,
+                                            pad_key=pad_key)
         self.wpsm_triton = TritonLinearHead(n_heads, causal=causal, output_value=float("-inf"))
         self.mta_conv_after_sm_triton = Conv2dTriton(
-            n_heads, kernel_size=(mta.after_sm_query_kernel_size, mta.after_sm_key_kernel_size), causal=causal)
+            n_heads, kernel_size=(mta.after_sm_query_kernel_size, mta.after_sm_key_kernel_size), causal=causal,
+            pad_key=pad_key)
         self.wposm_triton = TritonLinearHead(n_heads, causal=causal)
 
-        self.pad_key = mta.pad_key
+        self.pad_key = pad_key
         self.mta_init_method = mta.init_method
 
     def forward(self, xq, xk, xv, mask=None, chunk_start_ids=None):
@@ -58,8 +63,8 @@ class MTAAttentionTriton(nn.Module):
         dropping = self.training and self.dropout > 0.0
         if self.fused and not dropping and not (torch.is_grad_enabled() and any(
                 t.requires_grad for t in (xq, xk, xv, *self.parameters()))):
-            out = ops.mta_fused_fwd(xq, xk, xv, self.mta_conv_triton.weight, self.wpsm_triton.weight,
-                                    self.mta_conv_after_sm_triton.weight, self.wposm_triton.weight, causal=True)
+            out = ops.mta_fused_fwd(xq, xk, xv, self.mta_conv_triton.effective_weight(), self.wpsm_triton.weight,
+                                    self.mta_conv_after_sm_triton.effective_weight(), self.wposm_triton.weight, causal=True)
             return out.transpose(1, 2)
         # stage by stage; every stage is differentiable (the conv and the head mix through their backward kernels, the
         # scores, the softmax and the product with V through autograd_ops), so this is the path a training step uses
@@ -124,8 +129,9 @@ class MTAAttentionTriton(nn.Module):
         computation chunk by chunk, and the result comes back as a host tensor, (B,S,H,D) view as forward returns."""
         if not self.causal:
             raise NotImplementedError("MTAAttentionTriton without a mask requires causal=True, as in the reference's benchmarks")
-        o = ops.mta_fused_fwd_host(xq, xk, xv, self.mta_conv_triton.weight, self.wpsm_triton.weight,
-                                   self.mta_conv_after_sm_triton.weight, self.wposm_triton.weight, causal=True, out=out,
+        o = ops.mta_fused_fwd_host(xq, xk, xv, self.mta_conv_triton.effective_weight().detach(), self.wpsm_triton.weight,
+                                   self.mta_conv_after_sm_triton.effective_weight().detach(), self.wposm_triton.weight,
+                                   causal=True, out=out,
                                    chunk_batch=chunk_batch)
         return o.transpose(1, 2)
 

@@ -37,6 +37,7 @@ def lib() -> ctypes.CDLL:
         fp = ctypes.POINTER(ctypes.c_float)
         i = ctypes.c_int
         L.mta_oracle_conv2d.argtypes = [fp, fp, fp, i, i, i, i, i, i, i, i]
+        L.mta_oracle_conv2d_key_lead.argtypes = [fp, fp, fp, i, i, i, i, i, i, i, i, i]
         L.mta_oracle_head_linear.argtypes = [fp, fp, fp, i, i, i, i, i, ctypes.c_float, i]
         L.mta_oracle_softmax.argtypes = [fp, fp, ctypes.c_long, i, i, i, i]
         dp = ctypes.POINTER(ctypes.c_double)
@@ -48,7 +49,7 @@ def lib() -> ctypes.CDLL:
         L.mta_oracle_mta_fwd_rows.argtypes = [fp] * 7 + [i] * 13 + [fp]
         L.mta_oracle_conv_attn_fwd_rows.argtypes = [fp] * 4 + [i] * 7 + [ctypes.c_float] + [i] * 4 + [fp]
         L.mta_oracle_set_threads.argtypes = [i]
-        for name in ("mta_oracle_conv2d", "mta_oracle_head_linear", "mta_oracle_softmax",
+        for name in ("mta_oracle_conv2d", "mta_oracle_conv2d_key_lead", "mta_oracle_head_linear", "mta_oracle_softmax",
                      "mta_oracle_mta_fwd_rows", "mta_oracle_conv_attn_fwd_rows",
                      "mta_oracle_num_threads", "mta_oracle_abi_version"):
             getattr(L, name).restype = i
@@ -84,14 +85,38 @@ def round_to(a, mode: int) -> np.ndarray:
     return out
 
 
-def conv2d(x, w, causal: bool, round_mode: int = ROUND_NONE) -> np.ndarray:
-    """Depthwise causal conv on (N,C,H,W) with weight (C,R,S)."""
+def key_lead(pad_key: str, S: int) -> int:
+    """Left padding of the key axis for a kernel of width S (mta_attention_pytorch.py:91-103)."""
+    if pad_key == "both":
+        return (S - 1) // 2
+    if pad_key == "left":
+        return S - 1
+    if pad_key == "right":
+        return 0
+    raise ValueError(f"pad_key {pad_key!r}")
+
+
+def embed_pad_key(w, pad_key: str) -> np.ndarray:
+    """A (C,R,S) kernel applied with pad_key "left" / "right" equals the (C,R,2S-1) kernel with zero taps on the other
+    side applied with pad_key "both"; "both" returns w unchanged."""
+    w = _f32(w)
+    if pad_key == "both":
+        return w
+    S = w.shape[-1]
+    pad = ((0, 0), (0, 0), (0, S - 1)) if pad_key == "left" else ((0, 0), (0, 0), (S - 1, 0))
+    assert pad_key in ("left", "right")
+    return np.ascontiguousarray(np.pad(w, pad))
+
+
+def conv2d(x, w, causal: bool, round_mode: int = ROUND_NONE, pad_key: str = "both") -> np.ndarray:
+    """Depthwise causal conv on (N,C,H,W) with weight (C,R,S); pad_key places the key window."""
     x, w = _f32(x), _f32(w)
     N, C, H, W = x.shape
     Cw, R, S = w.shape
     assert Cw == C
     y = np.empty_like(x)
-    _check(lib().mta_oracle_conv2d(_p(x), _p(w), _p(y), N, C, H, W, R, S, int(causal), round_mode), "conv2d")
+    _check(lib().mta_oracle_conv2d_key_lead(_p(x), _p(w), _p(y), N, C, H, W, R, S, int(causal), round_mode,
+                                            key_lead(pad_key, S)), "conv2d")
     return y
 
 
@@ -156,9 +181,10 @@ def softmax(x, causal: bool = True, round_mode: int = ROUND_NONE) -> np.ndarray:
 
 
 def mta_fwd_rows(q, k, v, w1, W1, w2, W2, b: int, r0: int, r1: int, causal: bool = True,
-                 round_mode: int = ROUND_NONE) -> np.ndarray:
-    """Full MTA forward for batch element b, rows [r0,r1): returns (H, r1-r0, D)."""
-    q, k, v, w1, W1, w2, W2 = map(_f32, (q, k, v, w1, W1, w2, W2))
+                 round_mode: int = ROUND_NONE, pad_key: str = "both") -> np.ndarray:
+    """Full MTA forward for batch element b, rows [r0,r1): returns (H, r1-r0, D).  pad_key "left" / "right" goes in as
+    the equivalent zero-extended kernel (embed_pad_key; conv2d above has the direct form to check it against)."""
+    q, k, v, w1, W1, w2, W2 = map(_f32, (q, k, v, embed_pad_key(w1, pad_key), W1, embed_pad_key(w2, pad_key), W2))
     B, H, S, D = q.shape
     _, cq, ck = w1.shape
     _, cq2, ck2 = w2.shape
@@ -169,11 +195,12 @@ def mta_fwd_rows(q, k, v, w1, W1, w2, W2, b: int, r0: int, r1: int, causal: bool
     return out
 
 
-def mta_fwd(q, k, v, w1, W1, w2, W2, causal: bool = True, round_mode: int = ROUND_NONE) -> np.ndarray:
+def mta_fwd(q, k, v, w1, W1, w2, W2, causal: bool = True, round_mode: int = ROUND_NONE,
+            pad_key: str = "both") -> np.ndarray:
     """Full MTA forward: returns (B,H,S,D) (the reference returns its (B,S,H,D) transpose view)."""
     q = _f32(q)
     B, H, S, D = q.shape
-    return np.stack([mta_fwd_rows(q, k, v, w1, W1, w2, W2, b, 0, S, causal, round_mode) for b in range(B)])
+    return np.stack([mta_fwd_rows(q, k, v, w1, W1, w2, W2, b, 0, S, causal, round_mode, pad_key) for b in range(B)])
 
 
 def conv_attn_fwd_rows(q, k, v, w, b: int, r0: int, r1: int, causal: bool = True,
@@ -197,7 +224,7 @@ def conv_attn_fwd(q, k, v, w, causal: bool = True, softmax_scale: Optional[float
     return np.stack([conv_attn_fwd_rows(q, k, v, w, b, 0, S, causal, softmax_scale, round_mode) for b in range(B)])
 
 
-def mta_fwd_masked(q, k, v, w1, W1, w2, W2, mask, causal: bool = True) -> np.ndarray:
+def mta_fwd_masked(q, k, v, w1, W1, w2, W2, mask, causal: bool = True, pad_key: str = "both") -> np.ndarray:
     """The explicit-mask forward (mta_attention_triton.py:63-92 with use_mask=True; with a mask that contains the causal
     part it equals mta_attention_pytorch.py:56-83): mask (B,H,S,S) of 0 / -inf.  Full score planes in float64 / the C
     primitives above; returns (B,H,S,D) float32.  Small sizes only."""
@@ -205,12 +232,12 @@ def mta_fwd_masked(q, k, v, w1, W1, w2, W2, mask, causal: bool = True) -> np.nda
     mask = np.broadcast_to(_f32(mask), (q.shape[0], q.shape[1], q.shape[2], k.shape[2]))
     dead = np.isneginf(mask)
     scores = (np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), k.astype(np.float64)) / np.sqrt(q.shape[-1])).astype(np.float32)
-    scores = conv2d(np.where(dead, 0.0, scores).astype(np.float32), w1, causal)
+    scores = conv2d(np.where(dead, 0.0, scores).astype(np.float32), w1, causal, pad_key=pad_key)
     scores = head_linear(scores, W1, causal, float("-inf"))
     with np.errstate(invalid="ignore"):
         scores = (scores + mask).astype(np.float32)
     probs = softmax(scores, causal=False)
-    probs = conv2d(np.where(dead, 0.0, probs).astype(np.float32), w2, causal)
+    probs = conv2d(np.where(dead, 0.0, probs).astype(np.float32), w2, causal, pad_key=pad_key)
     probs = np.where(dead, 0.0, probs).astype(np.float32)
     probs = head_linear(probs, W2, causal, 0.0)
     return np.einsum("bhqk,bhkd->bhqd", probs.astype(np.float64), v.astype(np.float64)).astype(np.float32)

@@ -82,6 +82,27 @@ MASK_CASES = {
 MASK_GOLDEN = "golden_masked.npz"
 
 
+# pad_key = "left" / "right" cases (only the reference's PyTorch module places the key window there,
+# mta_attention_pytorch.py:91-98): name -> (MTA workload, pad_key, mask kind).  Forward outputs for all of them; for
+# the float32 cases without a mask also the full-module gradients, upstream gradient seeded with seed + 2000.
+PADKEY_WORKLOADS = {
+    "ragged_f32": MTA_CASES["ragged_f32"],
+    "s130_6x11_bf16": MTA_CASES["s130_6x11_bf16"],
+    "even_f32": MTAWorkload("even_f32", 2, 3, 37, 16, 3, 4, 2, 2, f32, 71, mix_var=0.05, random_post_conv=True),
+}
+PADKEY_CASES = {
+    "ragged_left": ("ragged_f32", "left", "none"),
+    "ragged_right": ("ragged_f32", "right", "none"),
+    "even_left": ("even_f32", "left", "none"),
+    "even_right": ("even_f32", "right", "none"),
+    "s130_bf16_left": ("s130_6x11_bf16", "left", "none"),
+    "s130_bf16_right": ("s130_6x11_bf16", "right", "none"),
+    "ragged_left_documents": ("ragged_f32", "left", "documents"),
+    "ragged_right_documents": ("ragged_f32", "right", "documents"),
+}
+PADKEY_GOLDEN = "golden_padkey.npz"
+
+
 def make_mask(kind: str, S: int, dtype):
     """The mask argument of forward for a mask case (None, (1,S) bool, or (1,1,S,S) additive in `dtype`)."""
     if kind == "none":
