@@ -1,10 +1,12 @@
 """Micro-benchmarks of the stand-alone kernels on the configurations their roofline targets are quoted on.
 
-    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|mix_softmax|qk|pv|backward|conv_attn|all] [--variant V]
+    python -m multitokenatention_triton_b200.microbench [conv2d|head_linear|softmax|mix_softmax|qk|pv|backward|conv_attn|graph|all] [--variant V]
                                                         [--batch N] [--seq S] [--iters K]
 
   conv2d       causal depthwise conv 6x11 on a (B=4, H=16, S=2048, S) bf16 score plane
   head_linear  16x16 head mix on post-softmax probabilities of the same shape
+  graph        the whole forward (five launches) at --batch/--heads/--seq/--dim, launched call by call and replayed
+               from a CUDA graph: what stream capture saves where the forward is launch-bound (not part of "all")
 
 Each kernel is timed alone with CUDA events on the launching stream (3 warm-up launches, then K timed ones;
 input + output of one launch exceed the 126 MB L2).  One JSON line per kernel:
@@ -63,7 +65,7 @@ def _line(name, ms, nbytes=None, flops=None, **extra):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "mix_softmax", "qk", "pv", "backward", "conv_attn", "all"])
+    ap.add_argument("which", nargs="?", default="all", choices=["conv2d", "head_linear", "softmax", "mix_softmax", "qk", "pv", "backward", "conv_attn", "graph", "all"])
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--heads", type=int, default=16)
@@ -156,6 +158,33 @@ def main():
         ms = _time(lambda: ops.conv_attn_fwd(q, k, v, w, True, D ** -0.5), a.iters)
         _line("conv attention 6x11 causal", ms, flops=(4.0 * D + 2.0 * 66) * N * C * tri, shape=shape + f" D{D}",
               tokens_per_s=N * S / (ms * 1e-3))
+    if a.which == "graph":
+        from .synthetic import MTAWorkload, make_mta_inputs
+        wl = MTAWorkload("graph", N, C, S, D, 6, 11, 3, 3, dtype, 3, random_post_conv=True)
+        t = {k: v.to(dev) for k, v in make_mta_inputs(wl).items()}
+        out = torch.empty_like(t["q"])
+        nbytes = _lib.lib().mta_workspace_bytes(N, C, S, D, 6, 11, 3, 3, 0, S, _lib.dtype_code(t["q"]))
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
+
+        def run():
+            ops.mta_fused_fwd(t["q"], t["k"], t["v"], t["w1"], t["W1"], t["w2"], t["W2"], True, out=out, workspace=ws)
+        run()                                                  # first call: per-device setup, before any capture
+        _lib.device_status()
+        eager = _time(run, a.iters)
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            run()
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                run()
+        torch.cuda.synchronize()
+        ref = out.clone()
+        out.zero_()
+        replay = _time(graph.replay, a.iters)
+        print(json.dumps({"kernel": "full forward, call by call against CUDA-graph replay", "shape": shape + f" D{D}",
+                          "ms_eager": eager, "ms_graph": replay, "bit_identical": bool(torch.equal(out, ref)),
+                          "tokens_per_s_graph": N * S / (replay * 1e-3)}), flush=True)
     _lib.device_status()
 
 
