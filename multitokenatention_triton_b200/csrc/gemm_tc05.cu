@@ -262,7 +262,10 @@ qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 // ------------------------------------------------------------------------------------------------
 // O tile = sum over key tiles of P tile x V tile.  Warp 0: TMA producer; warp 1: zeroes the part of a
 // diagonal P tile that lies above the diagonal, then issues the MMAs; warps 2..5: epilogue.
-constexpr int PV_STAGES = 3;
+#ifndef MTA_PV_STAGES
+#define MTA_PV_STAGES 3
+#endif
+constexpr int PV_STAGES = MTA_PV_STAGES;
 constexpr int PV_THREADS = 192;
 constexpr int PV_KEYS = 64;               // keys per pipeline stage: 32 KB stages, so two CTAs fit on an SM and one CTA's
                                           // start-up and epilogue overlap the other's steady state
