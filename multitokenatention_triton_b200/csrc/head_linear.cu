@@ -130,8 +130,12 @@ constexpr int MMA_KEYS_PER_WARP = 64;       // keys of one row handled per warp 
 // CP = padded head count (8, 16 or 32).  KSTEPS = CP/8 MMA k-steps, MT = number of 16-row output tiles.
 // SPLITW: the weight is float32 and is fed as two TF32 terms (high part + remainder), which keeps ~21 of
 // its mantissa bits; 16-bit weights are exact in TF32 and need one term.
+#ifndef MTA_HL_MIN_CTAS_WIDE
+#define MTA_HL_MIN_CTAS_WIDE 3     // resident CTAs per SM asked for when there are more than 16 heads (B1 H32 S8192 bf16:
+                                   // 1.015 ms unconstrained at 182 registers, 0.891 with 3, 1.869 with 4, which spills)
+#endif
 template <typename T, int CP, bool SPLITW>
-__global__ void __launch_bounds__(MMA_WARPS * 32)
+__global__ void __launch_bounds__(MMA_WARPS * 32, CP > 16 ? MTA_HL_MIN_CTAS_WIDE : 1)
 head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
                        T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
                        int row_end, int rows_per_cta, int write_upper, int w_transposed) {
@@ -355,8 +359,14 @@ template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float& l
 #ifndef MTA_MS_MIN_CTAS
 #define MTA_MS_MIN_CTAS 4          // resident CTAs per SM the register allocation aims at
 #endif
+#ifndef MTA_MS_MIN_CTAS_WIDE
+#define MTA_MS_MIN_CTAS_WIDE 3     // the same for more than 16 heads: twice the accumulators and weight fragments spill at
+                                   // 128 registers (B1 H32 S8192 bf16: 2.38 ms with 4, 1.67 with 3, 1.73 with 2)
+#endif
+constexpr int ms_min_ctas(int cp) { return cp > 16 ? MTA_MS_MIN_CTAS_WIDE : MTA_MS_MIN_CTAS; }
+
 template <typename T, int CP, bool SPLITW, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, MTA_MS_MIN_CTAS)
+__global__ void __launch_bounds__(WARPS * 32, ms_min_ctas(CP))
 head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype, T* y,
                         PlaneView yv, int C, int Q, int row_end, int write_upper) {
     constexpr int KSTEPS = CP / 8;
