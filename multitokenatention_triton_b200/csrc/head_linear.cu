@@ -134,11 +134,12 @@ constexpr int MMA_KEYS_PER_WARP = 64;       // keys of one row handled per warp 
 #define MTA_HL_MIN_CTAS_WIDE 3     // resident CTAs per SM asked for when there are more than 16 heads (B1 H32 S8192 bf16:
                                    // 1.015 ms unconstrained at 182 registers, 0.891 with 3, 1.869 with 4, which spills)
 #endif
+// The kernel body; the two __global__ entry points below differ only in their register bound.
 template <typename T, int CP, bool SPLITW>
-__global__ void __launch_bounds__(MMA_WARPS * 32, CP > 16 ? MTA_HL_MIN_CTAS_WIDE : 1)
-head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
-                       T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
-                       int row_end, int rows_per_cta, int write_upper, int w_transposed) {
+__device__ __forceinline__ void
+head_linear_mma_body(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
+                     T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
+                     int row_end, int rows_per_cta, int write_upper, int w_transposed) {
     constexpr int KSTEPS = CP / 8;
     constexpr int MT = (CP + 15) / 16;
     constexpr int NLOAD = CP / 4;            // head planes read per lane: t, t+4, ...
@@ -286,6 +287,26 @@ head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __rest
 #pragma unroll
         for (int j = 0; j < NLOAD; ++j) xr[j] = xn[j];
     }
+}
+
+// Up to 16 heads: no bound on resident CTAs (the compiler settles at 96 to 120 registers; stating a bound of one CTA
+// made it take far more and the kernel slower: 0.84 ms against 0.76 ms at B8 H16 S4096).
+template <typename T, int CP, bool SPLITW>
+__global__ void __launch_bounds__(MMA_WARPS * 32)
+head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
+                       T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
+                       int row_end, int rows_per_cta, int write_upper, int w_transposed) {
+    head_linear_mma_body<T, CP, SPLITW>(x, xv, Wm, w_dtype, y, yv, C, Q, causal, fill, row_begin, row_end, rows_per_cta,
+                                        write_upper, w_transposed);
+}
+// More than 16 heads: twice the accumulators and weight fragments; bounded so that MTA_HL_MIN_CTAS_WIDE CTAs stay resident.
+template <typename T, int CP, bool SPLITW>
+__global__ void __launch_bounds__(MMA_WARPS * 32, MTA_HL_MIN_CTAS_WIDE)
+head_linear_mma_wide_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
+                            T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
+                            int row_end, int rows_per_cta, int write_upper, int w_transposed) {
+    head_linear_mma_body<T, CP, SPLITW>(x, xv, Wm, w_dtype, y, yv, C, Q, causal, fill, row_begin, row_end, rows_per_cta,
+                                        write_upper, w_transposed);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -717,14 +738,18 @@ int launch_mma(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y
     const int rows_per_cta = rows >= 2048 ? 8 : (rows >= 256 ? 4 : 1);
     dim3 grid((unsigned)((Q + MMA_WARPS * MMA_KEYS_PER_WARP - 1) / (MMA_WARPS * MMA_KEYS_PER_WARP)),
               (unsigned)((rows + rows_per_cta - 1) / rows_per_cta), (unsigned)N);
-    if (w_dtype == MTA_F32)
-        head_linear_mma_kernel<T, CP, true><<<grid, MMA_WARPS * 32, 0, st>>>(
-            static_cast<const T*>(x), xv, Wm, w_dtype, static_cast<T*>(y), yv, C, Q, causal, fill, row_begin, row_end,
-            rows_per_cta, write_upper ? 1 : 0, wt ? 1 : 0);
-    else
-        head_linear_mma_kernel<T, CP, false><<<grid, MMA_WARPS * 32, 0, st>>>(
-            static_cast<const T*>(x), xv, Wm, w_dtype, static_cast<T*>(y), yv, C, Q, causal, fill, row_begin, row_end,
-            rows_per_cta, write_upper ? 1 : 0, wt ? 1 : 0);
+#define MTA_HL_LAUNCH(KERNEL, SPLIT)                                                                                     \
+    KERNEL<T, CP, SPLIT><<<grid, MMA_WARPS * 32, 0, st>>>(static_cast<const T*>(x), xv, Wm, w_dtype, static_cast<T*>(y), yv, C, \
+                                                         Q, causal, fill, row_begin, row_end, rows_per_cta,            \
+                                                         write_upper ? 1 : 0, wt ? 1 : 0)
+    if constexpr (CP > 16) {
+        if (w_dtype == MTA_F32) MTA_HL_LAUNCH(head_linear_mma_wide_kernel, true);
+        else MTA_HL_LAUNCH(head_linear_mma_wide_kernel, false);
+    } else {
+        if (w_dtype == MTA_F32) MTA_HL_LAUNCH(head_linear_mma_kernel, true);
+        else MTA_HL_LAUNCH(head_linear_mma_kernel, false);
+    }
+#undef MTA_HL_LAUNCH
     MTA_LAUNCH_OK("head_linear_mma_kernel");
     return MTA_OK;
 }
