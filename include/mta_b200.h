@@ -90,10 +90,14 @@ int mta_pv_fwd(const void* p, const void* v, void* o, int B, int H, int S, int D
  * mta_conv2d_fwd applied to the unscaled scores.
  * Replaces TritonAttention.forward + _attn_fwd (conv_attention_triton.py:362-452, :167-356);
  * oracle ConvAttention.forward (conv_attention_pytorch.py:36-91).
- *   q,k,v,o: (B,H,S,D) contiguous; w: (H,cq,ck).  Needs mta_conv_attn_workspace_bytes(...) bytes of
- *   caller-provided scratch (contents undefined on entry and exit).
+ *   q,k,v,o: (B,H,S,D) contiguous; w: (H,cq,ck).
+ * Causal 16-bit problems with D in {64,128} and an odd key extent <= 17 run as ONE kernel (scores, conv, online
+ * softmax and P V per key tile, as _attn_fwd_inner does, conv_attention_triton.py:21-147): no S x S tensor exists and
+ * mta_conv_attn_workspace_bytes(...) is 0 (workspace may be NULL).  Other problems (float32, non-causal, wider
+ * kernels) run stage by stage and need that many bytes of caller-provided scratch (two score planes; contents
+ * undefined on entry and exit).
  */
-size_t mta_conv_attn_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int dtype);
+size_t mta_conv_attn_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int causal, int dtype, int w_dtype);
 int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w, void* o, void* workspace,
                       size_t workspace_bytes, int B, int H, int S, int D, int cq, int ck, int causal,
                       float scale, int dtype, int w_dtype, void* stream);

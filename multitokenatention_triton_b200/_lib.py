@@ -40,7 +40,7 @@ SIGNATURES = {
     "mta_head_linear_bwd_weight": (_i, [_vp, _vp, _vp, _vp, _sz] + [_i] * 6 + [_vp]),
     "mta_qk_scores_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
     "mta_pv_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
-    "mta_conv_attn_workspace_bytes": (_sz, [_i] * 7),
+    "mta_conv_attn_workspace_bytes": (_sz, [_i] * 9),
     "mta_conv_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_static_scratch_bytes": (_sz, []),
     "mta_conv_attn_fwd_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),

@@ -52,7 +52,7 @@ using namespace mta;
 
 extern "C" {
 
-int mta_abi_version(void) { return 1; }
+int mta_abi_version(void) { return 2; }
 
 const char* mta_last_error(void) { return g_error; }
 

@@ -180,9 +180,15 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     return trace_end(st);
 }
 
-size_t mta_conv_attn_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int dtype) {
-    (void)D; (void)ck;
-    if (B <= 0 || H <= 0 || S <= 0 || cq < 1 || !dtype_ok(dtype)) return 0;
+// One kernel, no scratch: 16-bit dtypes the fused kernel takes (mta_set_variant("fused", 4) keeps the three-launch path).
+static bool conv_attn_one_kernel(int S, int D, int cq, int ck, int causal, int dtype, int w_dtype) {
+    return variant("fused") == 0 && variant("gemm") == 0 && variant("conv2d") == 0 &&
+           conv_attn_fused_shape_ok(S, D, cq, ck, causal, dtype, w_dtype);
+}
+
+size_t mta_conv_attn_workspace_bytes(int B, int H, int S, int D, int cq, int ck, int causal, int dtype, int w_dtype) {
+    if (B <= 0 || H <= 0 || S <= 0 || cq < 1 || !dtype_ok(dtype) || !dtype_ok(w_dtype)) return 0;
+    if (conv_attn_one_kernel(S, D, cq, ck, causal, dtype, w_dtype)) return 0;
     return 2 * make_plan(B, H, S, cq, 1, 0, S, dtype).buf_bytes;      // this path uses the two score planes only
 }
 
@@ -196,19 +202,25 @@ int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w
     if ((long)B * S == 0) return MTA_OK;
     MTA_REQUIRE(q && k && v && w && o, "conv_attn_fwd: null pointer");
     MTA_REQUIRE((long)B * H <= 65535, "conv_attn_fwd: B*H = %ld exceeds 65535", (long)B * H);
+    if (int rc = check_device()) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (conv_attn_one_kernel(S, D, cq, ck, causal, dtype, w_dtype)) {
+        MTA_REQUIRE(conv_attn_fused_supported(q, k, v, o, S, D, cq, ck, causal, dtype, w_dtype),
+                    "conv_attn_fwd: q, k, v and o must be 16-byte aligned");
+        // raw scores into the conv (score scale 1), the softmax scale after it, as the reference orders them
+        return conv_attn_fused_launch(q, k, v, w, w_dtype, o, B, H, S, D, cq, ck, 1.0f, scale, 0, S, dtype, st);
+    }
     const Plan pl = make_plan(B, H, S, cq, 1, 0, S, dtype);
     MTA_REQUIRE(workspace && workspace_bytes >= 2 * pl.buf_bytes, "conv_attn_fwd: workspace of %zu bytes is smaller than the %zu needed",
                 workspace_bytes, 2 * pl.buf_bytes);
     MTA_REQUIRE(aligned16(workspace), "conv_attn_fwd: workspace must be 16-byte aligned");
-    if (int rc = check_device()) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* bufA = workspace;
     void* bufB = static_cast<char*>(workspace) + pl.buf_bytes;
     const PlaneView pv{(long)S * S, 0, S};
     const long planes = (long)B * H;
     int rc;
     // 16-bit dtypes: the raw scores are computed inside the conv's kernel (scale 1: the conv attention scales after its conv)
-    if (variant("fused") == 0 && variant("gemm") == 0 && variant("conv2d") == 0 && planes <= 65535 &&
+    if ((variant("fused") == 0 || variant("fused") == 4) && variant("gemm") == 0 && variant("conv2d") == 0 && planes <= 65535 &&
         qk_conv_supported(q, k, bufB, pv, S, D, cq, ck, causal, dtype, w_dtype)) {
         if ((rc = qk_conv_launch(q, k, w, w_dtype, bufB, pv, B, H, S, D, cq, ck, 1.0f, 0, S, dtype, st))) return rc;
     } else {

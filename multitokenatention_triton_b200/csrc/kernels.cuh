@@ -96,6 +96,14 @@ bool qk_conv_supported(const void* q, const void* k, const void* y, PlaneView yv
                        int w_dtype);
 int qk_conv_launch(const void* q, const void* k, const void* w, int w_dtype, void* y, PlaneView yv, int B, int H, int S, int D,
                    int R, int KS, float scale, int row_begin, int row_end, int dtype, cudaStream_t st);
+// The conv attention forward softmax(sm_scale * conv(round(Q K^T * score_scale))) V in one kernel with no score plane
+// anywhere (conv_attn_tc05.cu); output rows [row_begin,row_end).  16-bit dtypes, D in {64,128}, odd key extent <= 17,
+// causal, any S.
+bool conv_attn_fused_shape_ok(int S, int D, int R, int KS, int causal, int dtype, int w_dtype);
+bool conv_attn_fused_supported(const void* q, const void* k, const void* v, const void* o, int S, int D, int R, int KS, int causal,
+                               int dtype, int w_dtype);
+int conv_attn_fused_launch(const void* q, const void* k, const void* v, const void* w, int w_dtype, void* o, int B, int H, int S, int D,
+                           int R, int KS, float score_scale, float sm_scale, int row_begin, int row_end, int dtype, cudaStream_t st);
 // Reads and clears the flag raised by a device-side bounded wait that gave up (synchronises `st`).
 int device_wait_status(cudaStream_t st, int* timed_out);
 

@@ -49,8 +49,8 @@ int mta_conv_attn_fwd_static(const void* q, const void* k, const void* v, const 
     MTA_REQUIRE(mta::dtype_ok(dtype) && B >= 0 && H >= 1 && S >= 0 && D >= 1 && cq >= 1 && ck >= 1,
                 "conv_attn_fwd_static: bad shape or dtype (B=%d H=%d S=%d D=%d cq=%d ck=%d dtype=%d)", B, H, S, D, cq, ck, dtype);
     if ((long)B * S == 0) return MTA_OK;
-    const size_t need = mta_conv_attn_workspace_bytes(B, H, S, D, cq, ck, dtype);
-    MTA_REQUIRE(need > 0 && need <= kStaticScratchBytes,
+    const size_t need = mta_conv_attn_workspace_bytes(B, H, S, D, cq, ck, causal, dtype, w_dtype);
+    MTA_REQUIRE(need <= kStaticScratchBytes,
                 "conv_attn_fwd_static: B=%d H=%d S=%d needs %zu bytes of scratch, the built-in array holds %zu; "
                 "use mta_conv_attn_fwd with a caller workspace for larger problems",
                 B, H, S, need, kStaticScratchBytes);

@@ -14,71 +14,21 @@
 //                      R-1 rows past the 128 staged ones; those only reach output rows >= TMO, which are not stored.
 //   epilogue (8 warps) TMEM -> 16-bit -> swizzled staging tile -> TMA store of TMO rows.
 // Warps: 0 TMA producer (Q tile per row of tiles, K tile per tile, double-buffered), 1 score-MMA issuer, 2-3 conv-MMA
-// issuers, 4-7 and 16-19 drain, 8-15 epilogue.  16-bit dtypes, D in {64, 128}, odd key extent <= 17, causal.
-#include <cstdlib>
-
-#include "kernels.cuh"
-#include "tc05.cuh"
+// issuers, 4-7 drain, 8-15 epilogue.  16-bit dtypes, D in {64, 128}, odd key extent <= 17, causal.
+#include "toeplitz_tc05.cuh"
 
 namespace mta {
 namespace {
 using namespace tc05;
+using namespace qc;
 
-// Per-role cycle counters of CTA 0, compiled in only with -DMTA_QC_PROFILE and printed by the launcher when the
-// environment variable MTA_QC_PROFILE is set.
-#ifdef MTA_QC_PROFILE
-__device__ long long g_qc_prof[32];
-#define QP_DECL long long qp_loc[4] = {0, 0, 0, 0}; long long qp_t = clock64();
-#define QP_ACC(slot) { const long long qp_n = clock64(); qp_loc[(slot) & 3] += qp_n - qp_t; qp_t = qp_n; }
-#define QP_FLUSH(base, cond) if (blockIdx.x == 0 && lane == 0 && (cond)) for (int pi = 0; pi < 4; ++pi) g_qc_prof[(base) + pi] = qp_loc[pi];
-#else
-#define QP_DECL
-#define QP_ACC(slot)
-#define QP_FLUSH(base, cond)
-#endif
-
-constexpr int TM = 128;            // staged rows = MMA M
-constexpr int TN = 128;            // output columns per tile
-constexpr int NB = TN / 16;
-constexpr int NKS = 9;             // k-steps of 16 staged columns
-constexpr int SN = 144;            // staged columns = N of the score MMA
-constexpr int BOX_BYTES = TM * 128;               // one 64-column box of the staged tile: 128 rows x 128 bytes
-constexpr int BOX3_BYTES = TM * 32;               // the 16-column box
 constexpr int OUT_BYTES = 2 * TM * 128;           // output staging: two 64-column boxes
-constexpr int KBOX_BYTES = SN * 128;              // one 64-element box of the K tile: 144 rows x 128 bytes (18 KB)
-// Drain warps: 4 (warps 4-7, a thread converts its whole staged row) or 8 (warps 16-19 take staged columns 72..143).
-// Measured at B8 H16 S4096 D128, 6 x 11: 4 warps with sleeping waits 1.26 ms, 8 warps with spinning waits 1.35 ms - the
-// kernel is bound by shared-memory bandwidth (the conv MMAs' operand reads, ~300 KB per tile, plus ~200 KB of tile
-// traffic), and extra polling and extra warps only add to it.
+// Four drain warps (warps 4-7): a thread converts its whole staged row.  Measured at B8 H16 S4096 D128, 6 x 11: 1.26 ms;
+// eight warps with spinning waits 1.35 ms - the kernel is bound by shared-memory bandwidth (the conv MMAs' operand
+// reads, ~300 KB per tile, plus ~200 KB of tile traffic), and extra polling and extra warps only add to it.
 constexpr int DRAIN_WARPS = 4;
-constexpr int THREADS = DRAIN_WARPS == 4 ? 512 : 640;
+constexpr int THREADS = 512;
 constexpr uint32_t S_COL = 256;                   // TMEM column of the score accumulator (conv accumulators: 0..255)
-
-template <typename T> struct AbFmtQ;
-template <> struct AbFmtQ<__nv_bfloat16> { static constexpr int value = 1; };
-template <> struct AbFmtQ<__half> { static constexpr int value = 0; };
-
-template <typename T> __device__ __forceinline__ uint32_t pack2q(float lo, float hi);
-template <> __device__ __forceinline__ uint32_t pack2q<__nv_bfloat16>(float lo, float hi) {
-    __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&r);
-}
-template <> __device__ __forceinline__ uint32_t pack2q<__half>(float lo, float hi) {
-    __half2 r = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&r);
-}
-
-__device__ __forceinline__ uint64_t desc_plain(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
-    d |= (uint64_t)1 << 46;
-    return d;
-}
-__device__ __forceinline__ void sts128q(uint32_t addr, const uint4& v) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 
 struct QcGeom {
     int C, S, R, KS, row_begin, row_end, tiles_n, tiles_m, tmo, split_w, y_row0;
@@ -117,39 +67,6 @@ struct QcIter {
     __device__ int n0() const { return tn * TN; }
 };
 
-// The conv MMAs of one tile for issuer ISSUER (blocks [b0, b1] of the eight 16-column output blocks): see
-// conv2d_tc05.cu for the schedule.
-template <typename T, int ISSUER>
-__device__ __forceinline__ void issue_conv(uint32_t xa_addr, uint32_t d0, int R, int split_w, int tb_off) {
-    constexpr uint32_t idesc32 = instr_desc_f16(AbFmtQ<T>::value, 0, 0, TM, 32);
-    constexpr uint32_t idesc16 = instr_desc_f16(AbFmtQ<T>::value, 0, 0, TM, 16);
-    constexpr int b0 = ISSUER == 0 ? 0 : 4, b1 = ISSUER == 0 ? 3 : 7;
-    const uint64_t da0 = smem_desc_sw128(xa_addr, 16, 1024);
-    const uint64_t da3 = smem_desc_sw32(xa_addr + (uint32_t)(2 * BOX_BYTES), 256);
-    const uint64_t db0 = desc_plain(xa_addr + (uint32_t)tb_off, 512, 128);
-    const int parts = split_w ? 2 : 1;
-    int batch = 0;
-#pragma unroll 1
-    for (int i = 0; i < R; ++i)
-#pragma unroll 1
-        for (int part = 0; part < parts; ++part, ++batch) {
-            const uint64_t db = db0 + (uint64_t)((i * 1024 + part * R * 1024) >> 4);
-            const uint64_t da = da0 + (uint64_t)((i * 128) >> 4);
-            const uint64_t dl = da3 + (uint64_t)((i * 32) >> 4);
-#pragma unroll
-            for (int pass = 0; pass < 2; ++pass)
-#pragma unroll
-                for (int s = b0 + 1 - pass; s <= b1 + 1; s += 2) {
-                    const bool upper = s == b0, lower = s == b1 + 1;
-                    const uint64_t adesc = s < 8 ? da + (uint64_t)(((s / 4) * BOX_BYTES + (s % 4) * 32) >> 4) : dl;
-                    const uint64_t bdesc = db + (upper ? 16u : 0u);
-                    const uint32_t dcol = upper ? 16u * (uint32_t)s : 16u * (uint32_t)(s - 1);
-                    const uint32_t acc = (batch > 0 || pass > 0) ? 1u : 0u;
-                    mma_f16_ss(d0 + dcol, adesc, bdesc, (upper || lower) ? idesc16 : idesc32, acc);
-                }
-        }
-}
-
 template <typename T, int D>
 __global__ void __launch_bounds__(THREADS, 1)
 qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
@@ -164,9 +81,7 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     const int R = g.R, KS = g.KS;
-    const int tb_bytes = (R * 1024 * (g.split_w ? 2 : 1) + 1023) & ~1023;
-    const int tb_off = 2 * BOX_BYTES + ((BOX3_BYTES + 1023) & ~1023);
-    const int stage_bytes = tb_off + tb_bytes;                 // staged score tile + Toeplitz slices
+    const int stage_bytes = qc::stage_bytes(R, g.split_w);     // staged score tile + Toeplitz slices
     uint8_t* out_base = smem;
     uint8_t* q_base = out_base + OUT_BYTES;
     uint8_t* k_base = q_base + Q_BYTES;
@@ -244,7 +159,6 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
         it.init(g, t_begin);
         bool new_q = true;
         int qn = 0;
-        QP_DECL
         for (int n = 0; n < my_tiles; ++n) {
             const int ks = n & 1;
             if (new_q) {
@@ -252,9 +166,7 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
                 ++qn;
             }
             mbar_wait(&k_full[ks], (n >> 1) & 1, err_flag);
-            QP_ACC(0)
             mbar_wait(&s_free, (n & 1) ^ 1, err_flag);           // the drain warps have read the previous score tile
-            QP_ACC(1)
             fence_after_sync();
             new_q = it.next(g);
             if (lane == 0) {
@@ -270,109 +182,48 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
                 if (new_q || n == my_tiles - 1) mma_commit(&q_free);     // last tile of this row of tiles
             }
             __syncwarp();
-            QP_ACC(2)
         }
-        QP_FLUSH(0, true)
     } else if (warp == 2 || warp == 3) {
         // ---------------- conv MMAs ----------------
-        QP_DECL
         for (int n = 0; n < my_tiles; ++n) {
             const int st = n & 1, ab = n & 1;
             mbar_wait(&ready_bar[st], (n >> 1) & 1, err_flag);
-            QP_ACC(0)
             mbar_wait(&acc_empty[ab], ((n >> 1) & 1) ^ 1, err_flag);
-            QP_ACC(1)
             fence_after_sync();
             if (lane == 0) {
                 const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
                 const uint32_t d0 = tmem + (uint32_t)(ab * TN);
-                if (warp == 2) issue_conv<T, 0>(xa_addr, d0, R, g.split_w, tb_off);
-                else issue_conv<T, 1>(xa_addr, d0, R, g.split_w, tb_off);
+                if (warp == 2) issue_conv<T, 0>(xa_addr, d0, R, g.split_w);
+                else issue_conv<T, 1>(xa_addr, d0, R, g.split_w);
                 mma_commit(&empty_bar[st]);
                 mma_commit(&acc_full[ab]);
             }
             __syncwarp();
-            QP_ACC(2)
         }
-        QP_FLUSH(4, warp == 2)
-    } else if (warp < 8 || warp >= 16) {
+    } else if (warp < 8) {
         // ---------------- drain: score tile TMEM -> rounded, scaled, masked -> staged tile; Toeplitz slices ----------------
         const int quarter = warp & 3;
-        const int first_half = warp >= 16 ? 1 : 0;           // first half of the staged columns this warp converts
         const int sr = quarter * 32 + lane;                  // staged row = TMEM lane of this thread
-        const int ft = warp < 8 ? tid - 128 : tid - 512 + 128;   // 0..255
+        const int ft = tid - 128;                            // 0..127
         const float sc = round_to<T>(g.scale);
         QcIter it;
         it.init(g, t_begin);
         int ph0 = -1, ph1 = -1;                              // head whose Toeplitz slices each stage holds
-        QP_DECL
         for (int n = 0; n < my_tiles; ++n, it.next(g)) {
             const int st = n & 1;
             const int m0 = it.m0(g), n0 = it.n0();
             const int head = it.plane % g.C;
             uint8_t* xa = stage_base + st * stage_bytes;
-            const uint32_t xa_s = smem_u32(xa);
             // the stage is free once the conv MMAs of tile n - 2 are done
             mbar_wait(&empty_bar[st], ((n >> 1) & 1) ^ 1, err_flag);
-            QP_ACC(0)
             int ph;
             if (st == 0) { ph = ph0; ph0 = head; } else { ph = ph1; ph1 = head; }
-            if (ph != head) {
-                uint8_t* tb = xa + tb_off;
-                const int total = R * 512;
-                for (int idx = ft; idx < total; idx += DRAIN_WARPS * 32) {
-                    const int i = idx / 512, e = idx % 512;
-                    const int nn = e / 16, kk = e % 16;
-                    const int j = kk + 16 - nn - a_off;
-                    const float wv = (j >= 0 && j < KS) ? load_weight(w, ((long)head * R + i) * KS + j, w_dtype) : 0.0f;
-                    const T hi = from_f32<T>(wv);
-                    const int off = i * 1024 + (kk / 8) * 512 + (nn / 8) * 128 + (nn % 8) * 16 + (kk % 8) * 2;
-                    *reinterpret_cast<T*>(tb + off) = hi;
-                    if (g.split_w) *reinterpret_cast<T*>(tb + R * 1024 + off) = from_f32<T>(wv - to_f32<T>(hi));
-                }
-            }
-            QP_ACC(1)
+            if (ph != head) build_toeplitz<T>(xa + TB_OFF, w, w_dtype, head, R, KS, a_off, g.split_w, ft, DRAIN_WARPS * 32);
             mbar_wait(&s_full, n & 1, err_flag);
-            QP_ACC(2)
             __syncwarp();
             fence_after_sync();
-            const int qq = m0 - lead + sr;                   // query of this staged row
-            const int kbase = n0 - 8;                        // key of staged column 0
-            const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16) + S_COL;
-            auto convert8 = [&](const uint32_t* r, int col) -> uint4 {      // staged columns col .. col + 7
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    f[e] = round_to<T>(__uint_as_float(r[e])) * sc;
-                    if (kbase + col + e > qq) f[e] = 0.0f;
-                }
-                return make_uint4(pack2q<T>(f[0], f[1]), pack2q<T>(f[2], f[3]), pack2q<T>(f[4], f[5]), pack2q<T>(f[6], f[7]));
-            };
-            auto store_chunk = [&](int ch, const uint4& v) {     // chunk ch = staged columns 8 ch .. 8 ch + 7
-                if (ch < 16) sts128q(xa_s + (uint32_t)((ch >> 3) * BOX_BYTES + sr * 128 + (((ch & 7) ^ (sr & 7)) << 4)), v);
-                else sts128q(xa_s + (uint32_t)(2 * BOX_BYTES + sr * 32 + ((((ch - 16) ^ (sr >> 2)) & 1) << 4)), v);
-            };
-            // nine chunks at a time: 0..8 (columns 0..71) then / or 9..17 (columns 72..143), as loads of 32 + 32 + 8 columns
-#pragma unroll 1
-            for (int chalf = first_half; chalf < 2; chalf += DRAIN_WARPS / 4) {
-            const int c0 = chalf * 9;
-#pragma unroll 1
-            for (int part = 0; part < 2; ++part) {
-                uint32_t r[32];
-                const int cfirst = chalf == 0 ? c0 + 4 * part : c0 + 1 + 4 * part;    // first chunk of this 32-column load
-                tmem_ld_32x32(trow + (uint32_t)(cfirst * 8), r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) store_chunk(cfirst + c4, convert8(r + 8 * c4, (cfirst + c4) * 8));
-            }
-            {
-                uint32_t r[8];
-                const int cl = chalf == 0 ? c0 + 8 : c0;                                  // the remaining chunk
-                tmem_ld_32x8(trow + (uint32_t)(cl * 8), r);
-                tmem_ld_wait();
-                store_chunk(cl, convert8(r, cl * 8));
-            }
-            }
+            // staged row sr is query m0 - lead + sr, staged column 0 is key n0 - 8
+            drain_row<T>(tmem + ((uint32_t)(quarter * 32) << 16) + S_COL, smem_u32(xa), sr, m0 - lead + sr, n0 - 8, sc);
             fence_before_sync();
             fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
             __syncwarp();
@@ -380,9 +231,7 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
                 mbar_arrive(&s_free);
                 mbar_arrive(&ready_bar[st]);
             }
-            QP_ACC(3)
         }
-        QP_FLUSH(8, warp == 4)
     } else {
         // ---------------- epilogue: warps 8-11 take columns 0..63, warps 12-15 columns 64..127 ----------------
         const int quarter = warp & 3;
@@ -391,18 +240,15 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
         const int row = quarter * 32 + lane;
         QcIter it;
         it.init(g, t_begin);
-        QP_DECL
         for (int n = 0; n < my_tiles; ++n, it.next(g)) {
             const int ab = n & 1;
             const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
             uint8_t* orow = out_base + half * (TM * 128) + row * 128;
             mbar_wait(&acc_full[ab], (n >> 1) & 1, err_flag);
-            QP_ACC(0)
             __syncwarp();
             fence_after_sync();
             if (issuer) bulk_wait_read();                    // the previous tile's store has finished reading the staging tile
             named_barrier(1, 256);
-            QP_ACC(1)
             const int q = m0 + row;
 #pragma unroll
             for (int cblk = 0; cblk < 2; ++cblk) {
@@ -432,7 +278,6 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[ab]);
-            QP_ACC(2)
             fence_proxy_async();
             named_barrier(1, 256);
             if (issuer) {
@@ -441,9 +286,7 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
                 if (n0 + 64 < g.S) tma_store_3d(&my, out_base + TM * 128, n0 + 64, m0 - g.y_row0, plane);
                 bulk_commit();
             }
-            QP_ACC(3)
         }
-        QP_FLUSH(12, warp == 8)
         if (issuer) bulk_wait_all();
     }
     fence_before_sync();
@@ -492,19 +335,6 @@ int launch_qc(const void* q, const void* k, const void* w, int w_dtype, void* y,
     const unsigned grid = (unsigned)std::min<long>(g.total_tiles, sms);
     qk_conv_tc05_kernel<T, D><<<grid, THREADS, smem, st>>>(mq, mk, my, w, w_dtype, g, flag);
     MTA_LAUNCH_OK("qk_conv_tc05_kernel");
-#ifdef MTA_QC_PROFILE
-    if (getenv("MTA_QC_PROFILE")) {
-        cudaDeviceSynchronize();
-        long long h[32], z[32] = {};
-        cudaMemcpyFromSymbol(h, g_qc_prof, sizeof(h));
-        cudaMemcpyToSymbol(g_qc_prof, z, sizeof(z));
-        const long n0 = (g.total_tiles + grid - 1) / grid;
-        fprintf(stderr, "qk_conv clk/tile (CTA 0, %ld tiles): score wait_kq %lld wait_s_free %lld issue %lld | conv wait_ready %lld wait_acc %lld "
-                "issue %lld | drain wait_stage %lld toeplitz %lld wait_s_full %lld convert %lld | epilogue wait_acc %lld wait_store %lld drain %lld store %lld\n",
-                n0, h[0] / n0, h[1] / n0, h[2] / n0, h[4] / n0, h[5] / n0, h[6] / n0, h[8] / n0, h[9] / n0, h[10] / n0, h[11] / n0,
-                h[12] / n0, h[13] / n0, h[14] / n0, h[15] / n0);
-    }
-#endif
     return MTA_OK;
 }
 

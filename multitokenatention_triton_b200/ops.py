@@ -190,7 +190,7 @@ def conv_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weight: tor
     w = _weight(weight, q, "weight")
     o = torch.empty_like(q)
     L = lib()
-    nbytes = L.mta_conv_attn_workspace_bytes(B, H, S, D, cq, ck, dtype_code(q))
+    nbytes = L.mta_conv_attn_workspace_bytes(B, H, S, D, cq, ck, int(bool(causal)), dtype_code(q), dtype_code(w))
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         check(L.mta_conv_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), o.data_ptr(), ws.data_ptr(),

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     for s in syms:
         assert hasattr(L, s), f"{s} is declared in include/mta_b200.h but not exported"
     assert set(_lib.SIGNATURES) == set(syms), "ctypes table and header disagree"
-    assert L.mta_abi_version() == 1
+    assert L.mta_abi_version() == 2
 
 
 def test_bad_arguments_are_rejected_without_a_device():

@@ -33,9 +33,10 @@ def run_static(d, wl, causal=True):
 def test_static_scratch_matches_workspace_entry_point_twice():
     L = _lib.lib()
     assert L.mta_static_scratch_bytes() == 64 << 20
-    cases = [MTAWorkload("na1", 1, 8, 1024, 128, 6, 11, dtype=torch.bfloat16, seed=71),     # 32 MiB of scratch
-             MTAWorkload("na2", 2, 4, 200, 64, 3, 5, dtype=torch.float16, seed=72),         # smaller: runs over stale contents
-             MTAWorkload("na3", 1, 2, 130, 32, 3, 3, dtype=torch.float32, seed=73)]         # CUDA-core path, ragged size
+    cases = [MTAWorkload("na1", 1, 8, 1024, 32, 3, 5, dtype=torch.float32, seed=71),        # exactly the 64 MiB the array holds
+             MTAWorkload("na2", 2, 4, 200, 64, 3, 19, dtype=torch.float16, seed=72),        # 19 taps wide: stage by stage, over stale contents
+             MTAWorkload("na3", 1, 2, 130, 32, 3, 3, dtype=torch.float32, seed=73),         # CUDA-core path, ragged size
+             MTAWorkload("na4", 1, 8, 1024, 128, 6, 11, dtype=torch.bfloat16, seed=74)]     # one-kernel path: no scratch at all
     for wl in cases:
         inp = make_mta_inputs(wl)
         d = {k: inp[k].to(DEV) for k in ("q", "k", "v", "w1")}
@@ -51,7 +52,9 @@ def test_static_scratch_matches_workspace_entry_point_twice():
 def test_static_scratch_rejects_oversized_problems():
     L = _lib.lib()
     one = ctypes.c_void_p(256)
-    rc = L.mta_conv_attn_fwd_static(one, one, one, one, one, 1, 16, 2048, 128, 6, 11, 1, 0.1, 1, 1, None)   # 256 MiB needed
+    rc = L.mta_conv_attn_fwd_static(one, one, one, one, one, 1, 16, 2048, 128, 6, 11, 1, 0.1, 0, 0, None)   # float32: 512 MiB needed
     assert rc == 1 and b"built-in array" in L.mta_last_error()
-    rc = L.mta_conv_attn_fwd_static(one, one, one, one, one, 0, 16, 2048, 128, 6, 11, 1, 0.1, 1, 1, None)   # empty batch: no-op
+    rc = L.mta_conv_attn_fwd_static(one, one, one, one, one, 1, 8, 1032, 32, 3, 5, 1, 0.1, 0, 0, None)      # a few rows over 64 MiB
+    assert rc == 1 and b"built-in array" in L.mta_last_error()
+    rc = L.mta_conv_attn_fwd_static(one, one, one, one, one, 0, 16, 2048, 128, 6, 11, 1, 0.1, 0, 0, None)   # empty batch: no-op
     assert rc == 0
