@@ -4,14 +4,15 @@
 //   scores     S[128 x 144] = Q[rows m0-(R-1) ..] . K[keys n0-8 ..]^T on tcgen05 into tensor memory (TMEM)
 //   drain      TMEM -> round(round(S) * score_scale), 0 above the diagonal -> the swizzled staged tile in shared memory
 //   conv       the Toeplitz MMAs of conv2d_tc05.cu over the staged tile -> TMEM accumulator (128 x 128 fp32)
-//   softmax    TMEM -> x = round(round(conv) * scale), -inf above the diagonal -> running (reference max, sum) per
-//              query row, P = 2^((x - m) log2 e) in the 16-bit dtype -> swizzled shared-memory tile.  The output
+//   softmax    TMEM -> y = conv * scale * log2 e in fp32, -inf above the diagonal -> running (reference max, sum) per
+//              query row, P = 2^(y - m) in the 16-bit dtype -> swizzled shared-memory tile.  The output
 //              accumulator is rescaled (in TMEM) only when the row maximum grew by more than 2^8 since the reference
 //              maximum was taken, so almost never after the first key tiles
 //   P.V        O[128 x D] += P[128 x 128] V[128 x D] on tcgen05, O stays in TMEM for the whole unit
 //   epilogue   O / row sum -> 16-bit -> global memory, once per unit (conv_attention_triton.py:352-356)
-// The rounding points are the reference's 16-bit ones (conv_attention_pytorch.py:48-70): scores, conv output and
-// scaled logits are rounded to the dtype, the softmax runs in fp32.
+// Rounding: the scores are rounded to the 16-bit dtype as the reference's matmul does (conv_attention_pytorch.py:48)
+// and so are the exponentials that enter P.V; the conv output and the scaled logits, which the reference rounds
+// too (:57-64), stay in fp32 here.
 //
 // Warps: 0 Q / K loads (Q per unit, K per tile) and score MMAs, 1 V loads and P.V MMAs, 2-3 conv MMAs (disjoint output
 // columns, so the result is bit-reproducible), 4-7 drain, 8-15 softmax + epilogue (a pair of warps per 32 rows, 64
@@ -33,7 +34,13 @@ constexpr uint32_t C_COL = 0, S_COL = 128, O_COL = 384;
 constexpr int P_BYTES = 2 * BOX_BYTES;       // P tile: two 64-key boxes of 128 rows x 128 bytes
 constexpr int VBOX_BYTES = TN * 128;         // one box of the V tile: 128 keys x 64 elements
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr float RESCALE_STEP = 8.0f / LOG2E; // the reference maximum moves when the row maximum exceeds it by 2^8
+constexpr float RESCALE_STEP = 8.0f;         // the reference logit moves when the row maximum (base 2) exceeds it by 8
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 struct CaGeom {
     int C, S, R, KS, row_begin, row_end, tiles_m, tmo, split_w;
@@ -185,6 +192,7 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         const int sr = quarter * 32 + lane;                  // staged row = TMEM lane of this thread
         const int ft = tid - 128;                            // 0..127
         const float sc = round_to<T>(g.score_scale);
+        const bool scaled = g.score_scale != 1.0f;           // raw scores (the conv attention) are rounded once
         int ph0 = -1, ph1 = -1;                              // head whose Toeplitz slices each stage holds
         int n = 0;
         CA_FOR_UNITS
@@ -199,7 +207,10 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                 mbar_wait(&s_full, n & 1, err_flag);
                 __syncwarp();
                 fence_after_sync();
-                drain_row<T>(tmem + ((uint32_t)(quarter * 32) << 16) + S_COL, smem_u32(xa), sr, m0 - lead + sr, tn * TN - 8, sc);
+                const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16) + S_COL;
+                const bool diag = tn * TN + SN - 9 > m0 - lead;              // some staged key lies above some staged query
+                if (scaled) drain_row<T, true>(trow, smem_u32(xa), sr, m0 - lead + sr, tn * TN - 8, sc, diag);
+                else drain_row<T, false>(trow, smem_u32(xa), sr, m0 - lead + sr, tn * TN - 8, sc, diag);
                 fence_before_sync();
                 fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
                 __syncwarp();
@@ -211,49 +222,56 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         }
     } else if (warp >= 8) {
         // ---------------- softmax + epilogue: warps 8-11 take columns 0..63, warps 12-15 columns 64..127 ----------------
+        // The conv output stays in fp32 from the accumulator to the exponential (the reference rounds it to the 16-bit
+        // dtype twice on the way, conv_attention_pytorch.py:57-64); logits are handled in the base-2 domain:
+        // y = conv * (scale * log2 e), P = 2^(y - m).
         const int quarter = warp & 3;
         const int half = warp >= 12 ? 1 : 0;
         const int row = quarter * 32 + lane;                 // row of the tile = TMEM lane of this thread
         const uint32_t tlane = tmem + ((uint32_t)(quarter * 32) << 16);
-        const float sms = g.sm_scale;
+        const float c2 = g.sm_scale * LOG2E;
+        const bool neg = c2 < 0.0f;                          // a negative scale turns the row maximum into a minimum
+        const float masked = neg ? INFINITY : -INFINITY;     // raw value whose logit is -inf
         uint8_t* prow = p_base + half * BOX_BYTES + row * 128;
         int n = 0;
         CA_FOR_UNITS
             const int q = m0 + row;
-            float m_ref = -INFINITY;       // the maximum the exponentials of this row are taken against
+            float m_ref = -INFINITY;       // base-2 logit the exponentials of this row are taken against
             float l_part = 0.0f;           // sum of this thread's exponentials (its 64 columns of every tile)
             for (int tn = 0; tn < nk; ++tn, ++n) {
                 const int k0 = tn * TN + half * 64;          // key of this thread's first column
-                float x[64];
+                uint32_t xr[64];
                 mbar_wait(&acc_full, n & 1, err_flag);
                 __syncwarp();
                 fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tlane + C_COL + (uint32_t)(half * 64 + c * 32), r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) x[c * 32 + e] = round_to<T>(round_to<T>(__uint_as_float(r[e])) * sms);
-                }
+                tmem_ld_32x32(tlane + C_COL + (uint32_t)(half * 64), *reinterpret_cast<uint32_t(*)[32]>(&xr[0]));
+                tmem_ld_32x32(tlane + C_COL + (uint32_t)(half * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&xr[32]));
+                tmem_ld_wait();
                 fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty);
+                if (lane == 0) mbar_arrive(&acc_empty);      // the next tile's conv MMAs may overwrite the accumulator
+                float* x = reinterpret_cast<float*>(xr);
                 if (k0 + 63 > q) {
 #pragma unroll
                     for (int e = 0; e < 64; ++e)
-                        if (k0 + e > q) x[e] = -INFINITY;
+                        if (k0 + e > q) x[e] = masked;
                 }
                 float mx = x[0];
+                if (!neg) {
 #pragma unroll
-                for (int e = 1; e < 64; ++e) mx = fmaxf(mx, x[e]);
+                    for (int e = 1; e < 64; ++e) mx = fmaxf(mx, x[e]);
+                } else {
+#pragma unroll
+                    for (int e = 1; e < 64; ++e) mx = fminf(mx, x[e]);
+                }
+                mx *= c2;                                    // this half's largest logit (-inf when all are masked)
                 xch_max[n & 1][half][row] = mx;
-                named_barrier(1, 256);
+                named_barrier(1 + quarter, 64);              // the two warps that share these 32 rows
                 const float mt = fmaxf(mx, xch_max[n & 1][half ^ 1][row]);
                 float alpha = 1.0f;
                 bool moved = false;
                 if (mt - m_ref > RESCALE_STEP) {             // also the first tile (m_ref = -inf)
-                    alpha = m_ref == -INFINITY ? 0.0f : exp2f((m_ref - mt) * LOG2E);
+                    alpha = m_ref == -INFINITY ? 0.0f : ex2_approx(m_ref - mt);
                     m_ref = mt;
                     l_part *= alpha;
                     moved = true;
@@ -275,13 +293,13 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                     }
                     tmem_st_wait();
                 }
-                const float mb = m_ref == -INFINITY ? 0.0f : m_ref * LOG2E;
+                const float mb = m_ref == -INFINITY ? 0.0f : -m_ref;
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
                     float p[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        p[e] = exp2f(fmaf(x[c8 * 8 + e], LOG2E, -mb));
+                        p[e] = ex2_approx(fmaf(x[c8 * 8 + e], c2, mb));
                         l_part += p[e];
                     }
                     uint4 v;
@@ -301,7 +319,7 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
             __syncwarp();
             fence_after_sync();
             xch_sum[half][row] = l_part;
-            named_barrier(1, 256);
+            named_barrier(1 + quarter, 64);
             const float inv = 1.0f / (l_part + xch_sum[half ^ 1][row]);
             const bool store = row < g.tmo && q < g.row_end;
             T* orow = o + ((long)plane * g.S + (store ? q : 0)) * D + half * OH;

@@ -223,7 +223,9 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
             __syncwarp();
             fence_after_sync();
             // staged row sr is query m0 - lead + sr, staged column 0 is key n0 - 8
-            drain_row<T>(tmem + ((uint32_t)(quarter * 32) << 16) + S_COL, smem_u32(xa), sr, m0 - lead + sr, n0 - 8, sc);
+            // keys up to n0 + 135 are staged; the smallest query of the staged rows is m0 - lead
+            drain_row<T, true>(tmem + ((uint32_t)(quarter * 32) << 16) + S_COL, smem_u32(xa), sr, m0 - lead + sr, n0 - 8, sc,
+                               n0 + SN - 9 > m0 - lead);
             fence_before_sync();
             fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
             __syncwarp();

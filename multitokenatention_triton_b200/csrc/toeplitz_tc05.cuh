@@ -104,17 +104,21 @@ __device__ __forceinline__ void build_toeplitz(uint8_t* tb, const void* w, int w
     }
 }
 
-// One thread's share of the drain: staged row sr (query qq) of the score accumulator at TMEM address trow goes,
-// as round(round(S) * sc) with keys above the query zeroed, into the swizzled stage at shared-memory address xa_s
-// (staged column 0 holds key kbase).  Whole-warp call (the TMEM loads are warp-collective).
-template <typename T>
-__device__ __forceinline__ void drain_row(uint32_t trow, uint32_t xa_s, int sr, int qq, int kbase, float sc) {
+// One thread's share of the drain: staged row sr (query qq) of the score accumulator at TMEM address trow goes into the
+// swizzled stage at shared-memory address xa_s (staged column 0 holds key kbase).  SCALED: the staged value is
+// round(round(S) * sc), the reference's 16-bit matmul followed by its 16-bit multiply; otherwise round(S).  `diag`
+// (warp-uniform): the tile holds keys above some query of the row block, which are staged as 0; tiles wholly below the
+// diagonal skip the comparison.  Whole-warp call (the TMEM loads are warp-collective).
+template <typename T, bool SCALED>
+__device__ __forceinline__ void drain_row(uint32_t trow, uint32_t xa_s, int sr, int qq, int kbase, float sc, bool diag) {
     auto convert8 = [&](const uint32_t* r, int col) -> uint4 {      // staged columns col .. col + 7
         float f[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            f[e] = round_to<T>(__uint_as_float(r[e])) * sc;
-            if (kbase + col + e > qq) f[e] = 0.0f;
+        for (int e = 0; e < 8; ++e) f[e] = SCALED ? round_to<T>(__uint_as_float(r[e])) * sc : __uint_as_float(r[e]);
+        if (diag) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (kbase + col + e > qq) f[e] = 0.0f;
         }
         return make_uint4(pack2q<T>(f[0], f[1]), pack2q<T>(f[2], f[3]), pack2q<T>(f[4], f[5]), pack2q<T>(f[6], f[7]));
     };
