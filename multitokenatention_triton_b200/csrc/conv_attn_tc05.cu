@@ -5,10 +5,10 @@
 //   drain      TMEM -> round(round(S) * score_scale), 0 above the diagonal -> the swizzled staged tile in shared memory
 //   conv       the Toeplitz MMAs of conv2d_tc05.cu over the staged tile -> TMEM accumulator (128 x 128 fp32)
 //   softmax    TMEM -> y = conv * scale * log2 e in fp32, -inf above the diagonal -> running (reference max, sum) per
-//              query row, P = 2^(y - m) in the 16-bit dtype -> swizzled shared-memory tile.  The output
+//              query row, P = 2^(y - m) in the 16-bit dtype -> back into TMEM (never through shared memory).  The output
 //              accumulator is rescaled (in TMEM) only when the row maximum grew by more than 2^8 since the reference
 //              maximum was taken, so almost never after the first key tiles
-//   P.V        O[128 x D] += P[128 x 128] V[128 x D] on tcgen05, O stays in TMEM for the whole unit
+//   P.V        O[128 x D] += P[128 x 128] V[128 x D] on tcgen05 with P as the TMEM operand, O stays in TMEM for the whole unit
 //   epilogue   O / row sum -> 16-bit -> global memory, once per unit (conv_attention_triton.py:352-356)
 // Rounding: the scores are rounded to the 16-bit dtype as the reference's matmul does (conv_attention_pytorch.py:48)
 // and so are the exponentials that enter P.V; the conv output and the scaled logits, which the reference rounds
@@ -16,9 +16,12 @@
 //
 // Warps: 0 Q / K loads (Q per unit, K per tile) and score MMAs, 1 V loads and P.V MMAs, 2-3 conv MMAs (disjoint output
 // columns, so the result is bit-reproducible), 4-7 drain, 8-15 softmax + epilogue (a pair of warps per 32 rows, 64
-// columns each).  Every stage of the per-tile pipeline is its own role, so tile n+1's scores and drain overlap tile n's
-// conv MMAs, and tile n-1's softmax and P.V.
-// TMEM (512 columns): conv accumulator 0..127, score accumulator 128..271, O 384..384+D-1.
+// columns each).  Every stage of the per-tile pipeline is its own role and the staged tile has a ring of three
+// buffers, so the scores and the drain run up to two tiles ahead of the conv MMAs (the tensor pipe, which all three
+// kinds of MMA share, is the unit that limits the kernel), and the softmax and P.V follow one tile behind.
+// TMEM (512 columns): conv accumulator 0..127, score accumulator 128..271, P (16-bit, two keys per column) 272..335,
+// O 384..384+D-1.  The kernel is bound by shared-memory bandwidth (the conv MMAs re-read the staged tile once per row
+// tap), which is why P and nothing else that can avoid it goes through shared memory.
 // Work units are taken round-robin in the order (plane, heaviest row block first), so the CTAs that run at the same
 // time share a few planes' K and V through L2 and finish within one unit of one another.
 // 16-bit dtypes, D in {64, 128}, odd key extent <= 17, causal; any S (TMA zero-fills rows past the end).
@@ -30,8 +33,8 @@ using namespace tc05;
 using namespace qc;
 
 constexpr int CA_THREADS = 16 * 32;
-constexpr uint32_t C_COL = 0, S_COL = 128, O_COL = 384;
-constexpr int P_BYTES = 2 * BOX_BYTES;       // P tile: two 64-key boxes of 128 rows x 128 bytes
+constexpr int NSTAGE = 3;                   // staged score tiles in flight
+constexpr uint32_t C_COL = 0, S_COL = 128, P_COL = 272, O_COL = 384;
 constexpr int VBOX_BYTES = TN * 128;         // one box of the V tile: 128 keys x 64 elements
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;         // the reference logit moves when the row maximum (base 2) exceeds it by 8
@@ -66,19 +69,20 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     constexpr int OH = D / 2;                      // output columns per softmax warp
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t q_full, q_free, k_full, k_free, s_full, s_free, ready_bar[2], empty_bar[2], acc_full,
+    __shared__ __align__(8) uint64_t q_full, q_free, k_full, k_free, s_full, s_free, ready_bar[NSTAGE], empty_bar[NSTAGE], acc_full,
         acc_empty, v_full, p_ready, pv_done;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float xch_max[2][2][TM];           // [tile parity][column half][row]: a warp pair's halves of a row maximum
     __shared__ float xch_sum[2][TM];              // [column half][row]: the halves of a row sum, once per unit
+    __shared__ float wsm[MAX_TAPS];               // a head's conv weights on their way into the Toeplitz slices
     const int R = g.R, KS = g.KS;
-    const int stage_bytes = qc::stage_bytes(R, g.split_w);
-    uint8_t* p_base = smem;
-    uint8_t* q_base = p_base + P_BYTES;
+    const int tb_bytes = toeplitz_bytes(R, g.split_w);
+    uint8_t* q_base = smem;
     uint8_t* k_base = q_base + Q_BYTES;
     uint8_t* v_base = k_base + K_BYTES;
-    uint8_t* stage_base = v_base + V_BYTES;
+    uint8_t* stage_base = v_base + V_BYTES;        // NSTAGE staged tiles of TB_OFF bytes
+    uint8_t* tb_base = stage_base + NSTAGE * TB_OFF;     // two sets of Toeplitz slices: units alternate between them
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int a_off = 8 - (KS - 1) / 2;
     const int lead = R - 1;
@@ -95,7 +99,7 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
             mbar_init(&k_free, 1);
             mbar_init(&s_full, 1);
             mbar_init(&s_free, 4);
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < NSTAGE; ++i) {
                 mbar_init(&ready_bar[i], 4);
                 mbar_init(&empty_bar[i], 2);
             }
@@ -128,8 +132,9 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 
     if (warp == 0) {
         // ---------------- Q / K loads and score MMAs: S[128 x 144] = Q K^T into TMEM columns S_COL.. ----------------
-        // One thread does both: the K tile is single-buffered, so tile n's load can only be issued once the score MMAs
-        // of tile n - 1 have completed, which is this thread's own commit.
+        // One thread does both: the Q and K tiles are single-buffered, so a load can only be issued once the MMAs that
+        // read the buffer have completed, which is this thread's own commit.  The ring of staged tiles downstream
+        // keeps the conv MMAs fed while a load is in flight.
         constexpr uint32_t idesc = instr_desc_f16(AbFmtQ<T>::value, 0, 0, TM, SN);
         int n = 0, un = 0;
         CA_FOR_UNITS
@@ -169,22 +174,24 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         }
     } else if (warp == 2 || warp == 3) {
         // ---------------- conv MMAs ----------------
-        int n = 0;
+        int n = 0, un = 0;
         CA_FOR_UNITS
+            const uint32_t tb_addr = smem_u32(tb_base + (un & 1) * tb_bytes);
             for (int tn = 0; tn < nk; ++tn, ++n) {
-                const int st = n & 1;
-                mbar_wait(&ready_bar[st], (n >> 1) & 1, err_flag);
+                const int st = n % NSTAGE;
+                mbar_wait(&ready_bar[st], (n / NSTAGE) & 1, err_flag);
                 mbar_wait(&acc_empty, (n & 1) ^ 1, err_flag);    // the softmax warps have read the previous conv tile
                 fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
-                    if (warp == 2) issue_conv<T, 0>(xa_addr, tmem + C_COL, R, g.split_w);
-                    else issue_conv<T, 1>(xa_addr, tmem + C_COL, R, g.split_w);
+                    const uint32_t xa_addr = smem_u32(stage_base + st * TB_OFF);
+                    if (warp == 2) issue_conv<T, 0>(xa_addr, tb_addr, tmem + C_COL, R, g.split_w);
+                    else issue_conv<T, 1>(xa_addr, tb_addr, tmem + C_COL, R, g.split_w);
                     mma_commit(&empty_bar[st]);
                     mma_commit(&acc_full);
                 }
                 __syncwarp();
             }
+            ++un;
         }
     } else if (warp >= 4 && warp < 8) {
         // ---------------- drain: score tile TMEM -> rounded, scaled, masked -> staged tile; Toeplitz slices ----------------
@@ -193,17 +200,20 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         const int ft = tid - 128;                            // 0..127
         const float sc = round_to<T>(g.score_scale);
         const bool scaled = g.score_scale != 1.0f;           // raw scores (the conv attention) are rounded once
-        int ph0 = -1, ph1 = -1;                              // head whose Toeplitz slices each stage holds
-        int n = 0;
+        int n = 0, un = 0;
+        int tb_head[2] = {-1, -1};                           // head whose slices each of the two sets holds
         CA_FOR_UNITS
             const int head = plane % g.C;
+            if (tb_head[un & 1] != head) {
+                // this set was last read by the conv MMAs of unit un - 2, whose tiles all precede tile n - 1
+                if (n >= 2) mbar_wait(&empty_bar[(n - 2) % NSTAGE], ((n - 2) / NSTAGE) & 1, err_flag);
+                build_toeplitz<T>(tb_base + (un & 1) * tb_bytes, wsm, w, w_dtype, head, R, KS, a_off, g.split_w, ft, 128, 5);
+                tb_head[un & 1] = head;
+            }
             for (int tn = 0; tn < nk; ++tn, ++n) {
-                const int st = n & 1;
-                uint8_t* xa = stage_base + st * stage_bytes;
-                mbar_wait(&empty_bar[st], ((n >> 1) & 1) ^ 1, err_flag);     // conv MMAs of tile n - 2 are done
-                int ph;
-                if (st == 0) { ph = ph0; ph0 = head; } else { ph = ph1; ph1 = head; }
-                if (ph != head) build_toeplitz<T>(xa + TB_OFF, w, w_dtype, head, R, KS, a_off, g.split_w, ft, 128);
+                const int st = n % NSTAGE;
+                uint8_t* xa = stage_base + st * TB_OFF;
+                mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);   // conv MMAs of tile n - NSTAGE are done
                 mbar_wait(&s_full, n & 1, err_flag);
                 __syncwarp();
                 fence_after_sync();
@@ -219,6 +229,7 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                     mbar_arrive(&ready_bar[st]);
                 }
             }
+            ++un;
         }
     } else if (warp >= 8) {
         // ---------------- softmax + epilogue: warps 8-11 take columns 0..63, warps 12-15 columns 64..127 ----------------
@@ -232,7 +243,6 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         const float c2 = g.sm_scale * LOG2E;
         const bool neg = c2 < 0.0f;                          // a negative scale turns the row maximum into a minimum
         const float masked = neg ? INFINITY : -INFINITY;     // raw value whose logit is -inf
-        uint8_t* prow = p_base + half * BOX_BYTES + row * 128;
         int n = 0;
         CA_FOR_UNITS
             const int q = m0 + row;
@@ -294,22 +304,15 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                     tmem_st_wait();
                 }
                 const float mb = m_ref == -INFINITY ? 0.0f : -m_ref;
+                uint32_t pk[32];                             // this thread's 64 exponentials, two per column
 #pragma unroll
-                for (int c8 = 0; c8 < 8; ++c8) {
-                    float p[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        p[e] = ex2_approx(fmaf(x[c8 * 8 + e], c2, mb));
-                        l_part += p[e];
-                    }
-                    uint4 v;
-                    v.x = pack2q<T>(p[0], p[1]);
-                    v.y = pack2q<T>(p[2], p[3]);
-                    v.z = pack2q<T>(p[4], p[5]);
-                    v.w = pack2q<T>(p[6], p[7]);
-                    *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = v;
+                for (int e = 0; e < 32; ++e) {
+                    const float p0 = ex2_approx(fmaf(x[2 * e], c2, mb)), p1 = ex2_approx(fmaf(x[2 * e + 1], c2, mb));
+                    l_part += p0 + p1;
+                    pk[e] = pack2q<T>(p0, p1);
                 }
-                fence_proxy_async();          // the P tile is read by the MMAs (async proxy)
+                tmem_st_32x32(tlane + P_COL + (uint32_t)(half * 32), pk);
+                tmem_st_wait();
                 fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_ready);
@@ -359,12 +362,11 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                 __syncwarp();
                 fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t pa = smem_u32(p_base), va = smem_u32(v_base);
+                    const uint32_t va = smem_u32(v_base);
 #pragma unroll
                     for (int kk = 0; kk < TN / 16; ++kk) {
-                        const uint64_t da = smem_desc_sw128(pa + (kk / 4) * BOX_BYTES + (kk % 4) * 32, 16, 1024);
                         const uint64_t db = smem_desc_sw128(va + kk * 16 * 128, VBOX_BYTES, 1024);
-                        mma_f16_ss(tmem + O_COL, da, db, idesc, (tn > 0 || kk > 0) ? 1u : 0u);
+                        mma_f16_ts(tmem + O_COL, tmem + P_COL + (uint32_t)(kk * 8), db, idesc, (tn > 0 || kk > 0) ? 1u : 0u);
                     }
                     mma_commit(&pv_done);
                 }
@@ -379,7 +381,7 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 }
 
 size_t conv_attn_smem_bytes(int D, int R, bool split_w) {
-    return 1024 + P_BYTES + (size_t)(D / 64) * (BOX_BYTES + KBOX_BYTES + VBOX_BYTES) + 2 * (size_t)qc::stage_bytes(R, split_w ? 1 : 0);
+    return 1024 + (size_t)(D / 64) * (BOX_BYTES + KBOX_BYTES + VBOX_BYTES) + (size_t)NSTAGE * TB_OFF + 2 * (size_t)toeplitz_bytes(R, split_w ? 1 : 0);
 }
 
 template <typename T, int D>
@@ -411,7 +413,7 @@ int launch_ca(const void* q, const void* k, const void* v, const void* w, int w_
     return MTA_OK;
 }
 
-constexpr size_t CA_STATIC_SMEM = 4096;     // barriers and the exchange arrays, rounded up
+constexpr size_t CA_STATIC_SMEM = 4608;     // barriers, the exchange arrays and the weight buffer, rounded up
 constexpr size_t CA_SMEM_LIMIT = 227 * 1024;
 
 }  // namespace

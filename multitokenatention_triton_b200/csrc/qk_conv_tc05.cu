@@ -80,6 +80,7 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
         acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ float wsm[MAX_TAPS];                // the current head's conv weights on their way into the Toeplitz slices
     const int R = g.R, KS = g.KS;
     const int stage_bytes = qc::stage_bytes(R, g.split_w);     // staged score tile + Toeplitz slices
     uint8_t* out_base = smem;
@@ -193,8 +194,8 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
             if (lane == 0) {
                 const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
                 const uint32_t d0 = tmem + (uint32_t)(ab * TN);
-                if (warp == 2) issue_conv<T, 0>(xa_addr, d0, R, g.split_w);
-                else issue_conv<T, 1>(xa_addr, d0, R, g.split_w);
+                if (warp == 2) issue_conv<T, 0>(xa_addr, xa_addr + (uint32_t)TB_OFF, d0, R, g.split_w);
+                else issue_conv<T, 1>(xa_addr, xa_addr + (uint32_t)TB_OFF, d0, R, g.split_w);
                 mma_commit(&empty_bar[st]);
                 mma_commit(&acc_full[ab]);
             }
@@ -218,7 +219,7 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
             mbar_wait(&empty_bar[st], ((n >> 1) & 1) ^ 1, err_flag);
             int ph;
             if (st == 0) { ph = ph0; ph0 = head; } else { ph = ph1; ph1 = head; }
-            if (ph != head) build_toeplitz<T>(xa + TB_OFF, w, w_dtype, head, R, KS, a_off, g.split_w, ft, DRAIN_WARPS * 32);
+            if (ph != head) build_toeplitz<T>(xa + TB_OFF, wsm, w, w_dtype, head, R, KS, a_off, g.split_w, ft, DRAIN_WARPS * 32, 2);
             mbar_wait(&s_full, n & 1, err_flag);
             __syncwarp();
             fence_after_sync();

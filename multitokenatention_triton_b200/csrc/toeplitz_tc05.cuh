@@ -52,15 +52,16 @@ __host__ __device__ inline int toeplitz_bytes(int R, int split_w) { return (R * 
 __host__ __device__ inline int stage_bytes(int R, int split_w) { return TB_OFF + toeplitz_bytes(R, split_w); }
 
 // The conv MMAs of one tile for issuer ISSUER (blocks [b0, b1] of the eight 16-column output blocks): the schedule of
-// conv2d_tc05.cu over a stage at shared-memory address xa_addr, accumulating into TMEM columns d0 .. d0 + 127.
+// conv2d_tc05.cu over a staged tile at shared-memory address xa_addr with the Toeplitz slices at tb_addr, accumulating
+// into TMEM columns d0 .. d0 + 127.
 template <typename T, int ISSUER>
-__device__ __forceinline__ void issue_conv(uint32_t xa_addr, uint32_t d0, int R, int split_w) {
+__device__ __forceinline__ void issue_conv(uint32_t xa_addr, uint32_t tb_addr, uint32_t d0, int R, int split_w) {
     constexpr uint32_t idesc32 = instr_desc_f16(AbFmtQ<T>::value, 0, 0, TM, 32);
     constexpr uint32_t idesc16 = instr_desc_f16(AbFmtQ<T>::value, 0, 0, TM, 16);
     constexpr int b0 = ISSUER == 0 ? 0 : 4, b1 = ISSUER == 0 ? 3 : 7;
     const uint64_t da0 = smem_desc_sw128(xa_addr, 16, 1024);
     const uint64_t da3 = smem_desc_sw32(xa_addr + (uint32_t)(2 * BOX_BYTES), 256);
-    const uint64_t db0 = desc_plain(xa_addr + (uint32_t)TB_OFF, 512, 128);
+    const uint64_t db0 = desc_plain(tb_addr, 512, 128);
     const int parts = split_w ? 2 : 1;
     int batch = 0;
 #pragma unroll 1
@@ -87,21 +88,26 @@ __device__ __forceinline__ void issue_conv(uint32_t xa_addr, uint32_t d0, int R,
 // Writes the Toeplitz slices of `head` (row tap i, element (n', kk) = w[i][kk + 16 - n' - a_off]; with `split_w` a
 // second set holding what the 16-bit rounding of a float32 weight lost) in the no-swizzle K-major layout the conv
 // MMAs read: 8 rows x 16 bytes per core matrix, the two k chunks 512 bytes apart, row groups 128 bytes apart.
-// Called by `nthreads` threads with ft = 0 .. nthreads - 1.
+// Called by `nthreads` threads (whole warps, ft = 0 .. nthreads - 1) that own hardware barrier `bar_id`; the head's
+// R x KS weights pass through `wsm` (MAX_TAPS floats of shared memory) so that each is fetched from global memory once.
+constexpr int MAX_TAPS = 16 * 17;
 template <typename T>
-__device__ __forceinline__ void build_toeplitz(uint8_t* tb, const void* w, int w_dtype, int head, int R, int KS, int a_off,
-                                               int split_w, int ft, int nthreads) {
+__device__ __forceinline__ void build_toeplitz(uint8_t* tb, float* wsm, const void* w, int w_dtype, int head, int R, int KS,
+                                               int a_off, int split_w, int ft, int nthreads, int bar_id) {
+    for (int idx = ft; idx < R * KS; idx += nthreads) wsm[idx] = load_weight(w, (long)head * R * KS + idx, w_dtype);
+    named_barrier(bar_id, nthreads);
     const int total = R * 512;
     for (int idx = ft; idx < total; idx += nthreads) {
         const int i = idx / 512, e = idx % 512;
         const int nn = e / 16, kk = e % 16;
         const int j = kk + 16 - nn - a_off;
-        const float wv = (j >= 0 && j < KS) ? load_weight(w, ((long)head * R + i) * KS + j, w_dtype) : 0.0f;
+        const float wv = (j >= 0 && j < KS) ? wsm[i * KS + j] : 0.0f;
         const T hi = from_f32<T>(wv);
         const int off = i * 1024 + (kk / 8) * 512 + (nn / 8) * 128 + (nn % 8) * 16 + (kk % 8) * 2;
         *reinterpret_cast<T*>(tb + off) = hi;
         if (split_w) *reinterpret_cast<T*>(tb + R * 1024 + off) = from_f32<T>(wv - to_f32<T>(hi));
     }
+    named_barrier(bar_id, nthreads);        // nobody refills wsm while another warp still reads it
 }
 
 // One thread's share of the drain: staged row sr (query qq) of the score accumulator at TMEM address trow goes into the

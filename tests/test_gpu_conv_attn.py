@@ -23,7 +23,8 @@ CASES = {
     "s257_3x3": MTAWorkload("s257_3x3", 2, 2, 257, 64, 3, 3, dtype=bf16, seed=85),           # ragged S, three key tiles
     "s300_1x1": MTAWorkload("s300_1x1", 1, 2, 300, 128, 1, 1, dtype=f16, seed=86),           # plain attention
     "s515_6x11_f16": MTAWorkload("s515_6x11_f16", 1, 3, 515, 128, 6, 11, dtype=f16, seed=87),
-    "s640_9x17": MTAWorkload("s640_9x17", 1, 2, 640, 128, 9, 17, dtype=bf16, seed=88),       # largest kernel the tile takes
+    "s640_6x17": MTAWorkload("s640_6x17", 1, 2, 640, 128, 6, 17, dtype=bf16, seed=88),       # largest kernel the tile takes at D = 128
+    "s640_9x17_d64": MTAWorkload("s640_9x17_d64", 1, 2, 640, 64, 9, 17, dtype=bf16, seed=91),
     "s1024_h20": MTAWorkload("s1024_h20", 2, 20, 1024, 128, 6, 11, dtype=bf16, seed=89),     # more units than SMs
 }
 
