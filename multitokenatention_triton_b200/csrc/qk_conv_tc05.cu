@@ -13,7 +13,8 @@
 //                      issuers owning disjoint output blocks) into TMEM accumulator n % 2.  Row taps i > 0 read up to
 //                      R-1 rows past the 128 staged ones; those only reach output rows >= TMO, which are not stored.
 //   epilogue (8 warps) TMEM -> 16-bit -> swizzled staging tile -> TMA store of TMO rows.
-// Warps: 0 TMA producer (Q tile per row of tiles, K tile per tile, double-buffered), 1 score-MMA issuer, 2-3 conv-MMA
+// Warps: 0 TMA producer (Q tile per row of tiles, K tile per tile; a ring of three staged tiles hides the reloads),
+// 1 score-MMA issuer, 2-3 conv-MMA
 // issuers, 4-7 drain, 8-15 epilogue.  16-bit dtypes, D in {64, 128}, odd key extent <= 17, causal.
 #include "toeplitz_tc05.cuh"
 
@@ -23,6 +24,7 @@ using namespace tc05;
 using namespace qc;
 
 constexpr int OUT_BYTES = 2 * TM * 128;           // output staging: two 64-column boxes
+constexpr int NSTAGE = 3;                         // staged score tiles in flight
 // Four drain warps (warps 4-7): a thread converts its whole staged row.  Measured at B8 H16 S4096 D128, 6 x 11: 1.26 ms;
 // eight warps with spinning waits 1.35 ms - the kernel is bound by shared-memory bandwidth (the conv MMAs' operand
 // reads, ~300 KB per tile, plus ~200 KB of tile traffic), and extra polling and extra warps only add to it.
@@ -76,17 +78,18 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
     constexpr int K_BYTES = DBOX * KBOX_BYTES;                 // K tile: 144 keys x D
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t q_full, q_free, k_full[2], k_free[2], s_full, s_free, ready_bar[2], empty_bar[2],
+    __shared__ __align__(8) uint64_t q_full, q_free, k_full, k_free, s_full, s_free, ready_bar[NSTAGE], empty_bar[NSTAGE],
         acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ float wsm[MAX_TAPS];                // the current head's conv weights on their way into the Toeplitz slices
     const int R = g.R, KS = g.KS;
-    const int stage_bytes = qc::stage_bytes(R, g.split_w);     // staged score tile + Toeplitz slices
+    const int tb_bytes = toeplitz_bytes(R, g.split_w);
     uint8_t* out_base = smem;
     uint8_t* q_base = out_base + OUT_BYTES;
-    uint8_t* k_base = q_base + Q_BYTES;
-    uint8_t* stage_base = k_base + 2 * K_BYTES;
+    uint8_t* k_base = q_base + Q_BYTES;                        // one K tile: the ring of staged tiles hides its reload
+    uint8_t* stage_base = k_base + K_BYTES;                    // NSTAGE staged tiles of TB_OFF bytes
+    uint8_t* tb_base = stage_base + NSTAGE * TB_OFF;           // two sets of Toeplitz slices: successive heads alternate
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pad_w = (KS - 1) / 2;
     const int a_off = 8 - pad_w;
@@ -107,11 +110,13 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
             mbar_init(&q_free, 1);
             mbar_init(&s_full, 1);
             mbar_init(&s_free, DRAIN_WARPS);
-            for (int i = 0; i < 2; ++i) {
-                mbar_init(&k_full[i], 1);
-                mbar_init(&k_free[i], 1);
+            mbar_init(&k_full, 1);
+            mbar_init(&k_free, 1);
+            for (int i = 0; i < NSTAGE; ++i) {
                 mbar_init(&ready_bar[i], DRAIN_WARPS);
                 mbar_init(&empty_bar[i], 2);
+            }
+            for (int i = 0; i < 2; ++i) {
                 mbar_init(&acc_full[i], 2);
                 mbar_init(&acc_empty[i], 8);
             }
@@ -144,12 +149,10 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
                     for (int j = 0; j < DBOX; ++j) tma_load_3d(q_base + j * BOX_BYTES, &mq, &q_full, 64 * j, it.m0(g) - lead, it.plane);
                     ++qn;
                 }
-                const int ks = n & 1;
-                mbar_wait(&k_free[ks], ((n >> 1) & 1) ^ 1, err_flag);
-                mbar_expect_tx(&k_full[ks], (uint32_t)K_BYTES);
+                mbar_wait(&k_free, (n & 1) ^ 1, err_flag);       // the score MMAs of tile n - 1 have read the K tile
+                mbar_expect_tx(&k_full, (uint32_t)K_BYTES);
 #pragma unroll
-                for (int j = 0; j < DBOX; ++j)
-                    tma_load_3d(k_base + ks * K_BYTES + j * KBOX_BYTES, &mk, &k_full[ks], 64 * j, it.n0() - 8, it.plane);
+                for (int j = 0; j < DBOX; ++j) tma_load_3d(k_base + j * KBOX_BYTES, &mk, &k_full, 64 * j, it.n0() - 8, it.plane);
                 new_q = it.next(g);
             }
         }
@@ -161,24 +164,23 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
         bool new_q = true;
         int qn = 0;
         for (int n = 0; n < my_tiles; ++n) {
-            const int ks = n & 1;
             if (new_q) {
                 mbar_wait(&q_full, qn & 1, err_flag);
                 ++qn;
             }
-            mbar_wait(&k_full[ks], (n >> 1) & 1, err_flag);
+            mbar_wait(&k_full, n & 1, err_flag);
             mbar_wait(&s_free, (n & 1) ^ 1, err_flag);           // the drain warps have read the previous score tile
             fence_after_sync();
             new_q = it.next(g);
             if (lane == 0) {
-                const uint32_t qa = smem_u32(q_base), ka = smem_u32(k_base + ks * K_BYTES);
+                const uint32_t qa = smem_u32(q_base), ka = smem_u32(k_base);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t qoff = (kk / 4) * BOX_BYTES + (kk % 4) * 32, koff = (kk / 4) * KBOX_BYTES + (kk % 4) * 32;
                     mma_f16_ss(tmem + S_COL, smem_desc_sw128(qa + qoff, 16, 1024), smem_desc_sw128(ka + koff, 16, 1024), idesc,
                                kk > 0 ? 1u : 0u);
                 }
-                mma_commit(&k_free[ks]);
+                mma_commit(&k_free);
                 mma_commit(&s_full);
                 if (new_q || n == my_tiles - 1) mma_commit(&q_free);     // last tile of this row of tiles
             }
@@ -186,16 +188,22 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
         }
     } else if (warp == 2 || warp == 3) {
         // ---------------- conv MMAs ----------------
-        for (int n = 0; n < my_tiles; ++n) {
-            const int st = n & 1, ab = n & 1;
-            mbar_wait(&ready_bar[st], (n >> 1) & 1, err_flag);
+        QcIter it;
+        it.init(g, t_begin);
+        int cur_head = -1, hn = -1;                          // the running head and how many times it has changed
+        for (int n = 0; n < my_tiles; ++n, it.next(g)) {
+            const int st = n % NSTAGE, ab = n & 1;
+            const int head = it.plane % g.C;
+            if (head != cur_head) { cur_head = head; ++hn; }
+            mbar_wait(&ready_bar[st], (n / NSTAGE) & 1, err_flag);
             mbar_wait(&acc_empty[ab], ((n >> 1) & 1) ^ 1, err_flag);
             fence_after_sync();
             if (lane == 0) {
-                const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
+                const uint32_t xa_addr = smem_u32(stage_base + st * TB_OFF);
+                const uint32_t tb_addr = smem_u32(tb_base + (hn & 1) * tb_bytes);
                 const uint32_t d0 = tmem + (uint32_t)(ab * TN);
-                if (warp == 2) issue_conv<T, 0>(xa_addr, xa_addr + (uint32_t)TB_OFF, d0, R, g.split_w);
-                else issue_conv<T, 1>(xa_addr, xa_addr + (uint32_t)TB_OFF, d0, R, g.split_w);
+                if (warp == 2) issue_conv<T, 0>(xa_addr, tb_addr, d0, R, g.split_w);
+                else issue_conv<T, 1>(xa_addr, tb_addr, d0, R, g.split_w);
                 mma_commit(&empty_bar[st]);
                 mma_commit(&acc_full[ab]);
             }
@@ -209,24 +217,28 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
         const float sc = round_to<T>(g.scale);
         QcIter it;
         it.init(g, t_begin);
-        int ph0 = -1, ph1 = -1;                              // head whose Toeplitz slices each stage holds
+        int cur_head = -1, hn = -1;
         for (int n = 0; n < my_tiles; ++n, it.next(g)) {
-            const int st = n & 1;
+            const int st = n % NSTAGE;
             const int m0 = it.m0(g), n0 = it.n0();
             const int head = it.plane % g.C;
-            uint8_t* xa = stage_base + st * stage_bytes;
-            // the stage is free once the conv MMAs of tile n - 2 are done
-            mbar_wait(&empty_bar[st], ((n >> 1) & 1) ^ 1, err_flag);
-            int ph;
-            if (st == 0) { ph = ph0; ph0 = head; } else { ph = ph1; ph1 = head; }
-            if (ph != head) build_toeplitz<T>(xa + TB_OFF, wsm, w, w_dtype, head, R, KS, a_off, g.split_w, ft, DRAIN_WARPS * 32, 2);
+            uint8_t* xa = stage_base + st * TB_OFF;
+            if (head != cur_head) {
+                cur_head = head;
+                ++hn;
+                // this set of slices was read last by the conv MMAs of the head before the previous one: tiles <= n - 2
+                if (n >= 2) mbar_wait(&empty_bar[(n - 2) % NSTAGE], ((n - 2) / NSTAGE) & 1, err_flag);
+                build_toeplitz<T>(tb_base + (hn & 1) * tb_bytes, wsm, w, w_dtype, head, R, KS, a_off, g.split_w, ft, DRAIN_WARPS * 32, 2);
+            }
+            // the stage is free once the conv MMAs of tile n - NSTAGE are done
+            mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
             mbar_wait(&s_full, n & 1, err_flag);
             __syncwarp();
             fence_after_sync();
-            // staged row sr is query m0 - lead + sr, staged column 0 is key n0 - 8
-            // keys up to n0 + 135 are staged; the smallest query of the staged rows is m0 - lead
-            drain_row<T, true>(tmem + ((uint32_t)(quarter * 32) << 16) + S_COL, smem_u32(xa), sr, m0 - lead + sr, n0 - 8, sc,
-                               n0 + SN - 9 > m0 - lead);
+            // The causal comparison runs on every tile, also those wholly below the diagonal (measured: skipping it there
+            // made an earlier two-stage version of this kernel slower, because the drain's shared-memory stores then came
+            // in denser bursts and held up the operand reads of the conv MMAs).
+            drain_row<T, true>(tmem + ((uint32_t)(quarter * 32) << 16) + S_COL, smem_u32(xa), sr, m0 - lead + sr, n0 - 8, sc, true);
             fence_before_sync();
             fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
             __syncwarp();
@@ -298,9 +310,8 @@ qk_conv_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constan
 }
 
 size_t qk_conv_smem_bytes(int D, int R, bool split_w) {
-    const size_t tb = (size_t)((R * 1024 * (split_w ? 2 : 1) + 1023) & ~1023);
-    const size_t stage = 2 * BOX_BYTES + ((BOX3_BYTES + 1023) & ~1023) + tb;
-    return 1024 + OUT_BYTES + (size_t)(D / 64) * BOX_BYTES + 2 * (size_t)(D / 64) * KBOX_BYTES + 2 * stage;
+    return 1024 + OUT_BYTES + (size_t)(D / 64) * (BOX_BYTES + KBOX_BYTES) + (size_t)NSTAGE * TB_OFF +
+           2 * (size_t)toeplitz_bytes(R, split_w ? 1 : 0);
 }
 
 template <typename T, int D>

@@ -128,3 +128,22 @@ def make_upstream_grad(shape, dtype: torch.dtype, seed: int) -> torch.Tensor:
     """Seeded upstream gradient for the backward checks: N(0,1) drawn in float32 on the CPU, cast to `dtype`."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     return torch.randn(*shape, generator=g).to(dtype)
+
+
+def make_mta_weights(wl: MTAWorkload) -> Dict[str, torch.Tensor]:
+    """The four weights alone (w1, W1, w2, W2 in wl.dtype), drawn from their own generator so that they do not depend
+    on B, S or D: for runs whose q, k, v are drawn elsewhere (on the device, shard by shard)."""
+    g = torch.Generator(device="cpu").manual_seed(wl.seed + 7919)
+    var = wl.conv_var if wl.conv_var is not None else 1.0 / (wl.cq * wl.ck)
+    w1 = _conv_weight(g, wl.H, wl.cq, wl.ck, var, wl.identity_tap, True)
+    W1 = torch.eye(wl.H) + (wl.mix_var ** 0.5) * torch.randn(wl.H, wl.H, generator=g)
+    w2 = _conv_weight(g, wl.H, wl.cq2, wl.ck2, 1.0 / (wl.cq2 * wl.ck2), True, wl.random_post_conv)
+    W2 = torch.eye(wl.H) + (wl.mix_var ** 0.5) * torch.randn(wl.H, wl.H, generator=g)
+    return {k: t.to(wl.dtype) for k, t in {"w1": w1, "W1": W1, "w2": w2, "W2": W2}.items()}
+
+
+def device_qkv(wl: MTAWorkload, b: int, device) -> Dict[str, torch.Tensor]:
+    """q, k, v of batch element b, (1,H,S,D) in wl.dtype, drawn on `device` from a generator seeded by (wl.seed, b):
+    any rank can draw any batch element without drawing the others (not the values of make_mta_inputs)."""
+    g = torch.Generator(device=device).manual_seed(wl.seed * 1000003 + b)
+    return {n: torch.randn(1, wl.H, wl.S, wl.D, device=device, generator=g).to(wl.dtype) for n in ("q", "k", "v")}
