@@ -103,15 +103,20 @@ int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w
                       float scale, int dtype, int w_dtype, void* stream);
 
 /*
- * mta_conv_attn_fwd without a caller workspace (this entry point has no counterpart in the reference): the two
- * scratch score planes live in a 64 MiB array built into the library (MTA_STATIC_SCRATCH_BYTES, also returned by
- * mta_static_scratch_bytes()), for callers that must not or cannot allocate device memory.  Same arguments and
- * results as mta_conv_attn_fwd; returns 1 with a message when 2*B*H*S*S*elemsize (256-byte rounded per plane)
- * exceeds the array.  It allocates nothing.  The first call on each device looks up the array's device address
- * (do it before any stream capture).  All calls share the array: calls that overlap on the GPU race.
+ * mta_conv_attn_fwd without a caller workspace (this entry point has no counterpart in the reference), for callers
+ * that must not or cannot allocate device memory: a serving loop with a frozen memory pool, code running inside an
+ * allocator callback, a binding with no device buffers of its own.  Problems that mta_conv_attn_fwd runs as one kernel
+ * need no scratch here either; for the rest the two scratch score planes live in a 64 MiB array built into the library
+ * (MTA_STATIC_SCRATCH_BYTES, also returned by mta_static_scratch_bytes()).  Same arguments and results as
+ * mta_conv_attn_fwd; returns 1 with a message when mta_conv_attn_workspace_bytes(...) exceeds the array.
+ * It allocates nothing.  Looking up the array's device address is what makes the CUDA runtime place the 64 MiB on
+ * that device: mta_static_scratch_prepare() does that lookup for the current device and belongs at start-up, before
+ * the memory pool is frozen and before any stream capture (a first mta_conv_attn_fwd_static call would do it
+ * otherwise).  All calls share the array: calls that overlap on the GPU race.
  */
 #define MTA_STATIC_SCRATCH_BYTES ((size_t)64 << 20)
 size_t mta_static_scratch_bytes(void);
+int mta_static_scratch_prepare(void);
 int mta_conv_attn_fwd_static(const void* q, const void* k, const void* v, const void* w, void* o, int B, int H, int S,
                              int D, int cq, int ck, int causal, float scale, int dtype, int w_dtype, void* stream);
 
@@ -185,19 +190,28 @@ int mta_stage_times_ms(float* ms, const char** names, int capacity);
 /*
  * Synchronises `stream` and reports whether any kernel launched on this device since the last call gave
  * up a bounded device-side wait (returns 4 and clears the flag) - kernels never spin without limit.
+ * The condition is sticky until this call: the kernel that gave up also writes a word of page-locked host memory, and
+ * every compute entry point reads that word on entry (no synchronisation) and returns 4 without launching while it is
+ * set, so a forward issued after a timeout has reached the host cannot pass garbage off as a result.
  */
 int mta_device_status(void* stream);
+
+/* Fault injection on the host, for tests of the path above: marks the current device exactly as a kernel's timed-out
+ * wait would (no kernel is made to wait).  Until mta_device_status() clears it, kernels of this library return without
+ * computing and every compute entry point returns 4 (MTA_ERR_TIMEOUT) without launching. */
+int mta_inject_wait_timeout(void* stream);
 
 /* Number of kernel launches issued by this library on the calling thread since the last reset
  * (what a benchmark reports as its launch count). */
 long mta_launch_count(void);
 void mta_reset_launch_count(void);
 
-/* Selects implementation variants for A/B measurement: key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core;
- * key "conv2d" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core, 3 tcgen05 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core,
- * 2 tcgen05 tensor-core; key "fused" (mta_fused_fwd) -> 0 auto (Q K^T inside the first conv's kernel, the first
- * head mix and the softmax as one kernel), 1 strictly one kernel per stage, 2 fused conv + head-mix stages with the softmax
- * folded in (16-bit dtypes, H <= 16), 3 Q K^T and the first conv as two kernels, head mix + softmax as one.  Returns 0, or 1 for an unknown key/value. */
+/* Selects implementation variants for A/B measurement (process-wide, atomically updated, read on every launch):
+ * key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core; key "conv2d" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core,
+ * 3 tcgen05 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core, 2 tcgen05 tensor-core; key "fused"
+ * -> 0 auto (mta_fused_fwd: Q K^T inside the first conv's kernel, the first head mix and the softmax as one kernel;
+ * mta_conv_attn_fwd: one kernel), 1 strictly one kernel per stage, 2 the conv attention as three launches over score
+ * planes (needs the workspace), 3 Q K^T and the first conv as two kernels.  Returns 0, or 1 for an unknown key/value. */
 int mta_set_variant(const char* key, int value);
 
 #ifdef __cplusplus

@@ -11,8 +11,7 @@ from typing import Optional
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-# MTA_B200_LIB names another build of the same library (A/B runs of compile-time variants); default: the in-tree one.
-LIB_PATH = os.environ.get("MTA_B200_LIB") or os.path.join(_PKG, "libmta_b200.so")
+LIB_PATH = os.path.join(_PKG, "libmta_b200.so")
 
 MTA_F32, MTA_BF16, MTA_F16 = 0, 1, 2
 DTYPE_CODE = {torch.float32: MTA_F32, torch.bfloat16: MTA_BF16, torch.float16: MTA_F16}
@@ -27,6 +26,7 @@ SIGNATURES = {
     "mta_launch_count": (ctypes.c_long, []),
     "mta_reset_launch_count": (None, []),
     "mta_set_variant": (_i, [ctypes.c_char_p, _i]),
+    "mta_inject_wait_timeout": (_i, [_vp]),
     "mta_device_status": (_i, [_vp]),
     "mta_conv2d_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "mta_head_linear_fwd": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
@@ -43,6 +43,7 @@ SIGNATURES = {
     "mta_conv_attn_workspace_bytes": (_sz, [_i] * 9),
     "mta_conv_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_static_scratch_bytes": (_sz, []),
+    "mta_static_scratch_prepare": (_i, []),
     "mta_conv_attn_fwd_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_workspace_bytes": (_sz, [_i] * 11),
     "mta_fused_fwd": (_i, [_vp] * 9 + [_sz] + [_i] * 13 + [_vp]),

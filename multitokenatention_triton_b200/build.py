@@ -41,7 +41,7 @@ def _deps_mtime() -> float:
 
 
 def _compile(src: str, obj: str, verbose: bool) -> str:
-    cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("MTA_NVCC_EXTRA", "").split(), "-I", INCLUDE, "-c", src, "-o", obj]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

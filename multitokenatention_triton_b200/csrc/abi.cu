@@ -1,5 +1,6 @@
 // C ABI of the library: argument validation, error text, and dispatch to the kernel launchers.
 // See include/mta_b200.h for the contract of every entry point.
+#include <atomic>
 #include <cstring>
 #include <string>
 
@@ -9,10 +10,9 @@ namespace mta {
 namespace {
 thread_local char g_error[512] = "";
 thread_local long g_launches = 0;
-int g_variant_head_linear = 0;
-int g_variant_conv2d = 0;
-int g_variant_gemm = 0;
-int g_variant_fused = 0;
+// Kernel selection for tests and measurements: process-wide, read on every launch, written by mta_set_variant from any
+// thread (relaxed atomics: a launch sees either the old or the new value of each key, never a torn one).
+std::atomic<int> g_variant_head_linear{0}, g_variant_conv2d{0}, g_variant_gemm{0}, g_variant_fused{0};
 }  // namespace
 
 void set_error(const char* fmt, ...) {
@@ -25,10 +25,10 @@ void set_error(const char* fmt, ...) {
 void count_launch(int n) { g_launches += n; }
 
 int variant(const char* key) {
-    if (!strcmp(key, "head_linear")) return g_variant_head_linear;
-    if (!strcmp(key, "conv2d")) return g_variant_conv2d;
-    if (!strcmp(key, "gemm")) return g_variant_gemm;
-    if (!strcmp(key, "fused")) return g_variant_fused;
+    if (!strcmp(key, "head_linear")) return g_variant_head_linear.load(std::memory_order_relaxed);
+    if (!strcmp(key, "conv2d")) return g_variant_conv2d.load(std::memory_order_relaxed);
+    if (!strcmp(key, "gemm")) return g_variant_gemm.load(std::memory_order_relaxed);
+    if (!strcmp(key, "fused")) return g_variant_fused.load(std::memory_order_relaxed);
     return 0;
 }
 
@@ -40,6 +40,11 @@ int check_device() {
     if (major != 10) {
         set_error("device %d has compute capability %d.x; this library is built for sm_100a only", dev, major);
         return MTA_ERR_ARCH;
+    }
+    if (wait_flag_raised()) {
+        set_error("a bounded wait of an earlier kernel on device %d gave up: every kernel since then has returned without "
+                  "computing; mta_device_status() reports and clears the condition", dev);
+        return MTA_ERR_TIMEOUT;
     }
     return MTA_OK;
 }
@@ -61,10 +66,10 @@ void mta_reset_launch_count(void) { g_launches = 0; }
 
 int mta_set_variant(const char* key, int value) {
     if (!key || value < 0 || value > 3) return MTA_ERR_INVALID;
-    if (!strcmp(key, "head_linear")) g_variant_head_linear = value;
-    else if (!strcmp(key, "conv2d")) g_variant_conv2d = value;
-    else if (!strcmp(key, "gemm")) g_variant_gemm = value;
-    else if (!strcmp(key, "fused")) g_variant_fused = value;
+    if (!strcmp(key, "head_linear")) g_variant_head_linear.store(value, std::memory_order_relaxed);
+    else if (!strcmp(key, "conv2d")) g_variant_conv2d.store(value, std::memory_order_relaxed);
+    else if (!strcmp(key, "gemm")) g_variant_gemm.store(value, std::memory_order_relaxed);
+    else if (!strcmp(key, "fused")) g_variant_fused.store(value, std::memory_order_relaxed);
     else return MTA_ERR_INVALID;
     return MTA_OK;
 }
@@ -238,6 +243,11 @@ int mta_device_status(void* stream) {
         return MTA_ERR_TIMEOUT;
     }
     return MTA_OK;
+}
+
+int mta_inject_wait_timeout(void* stream) {
+    g_error[0] = 0;
+    return wait_flag_inject(static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -56,11 +56,14 @@ conv2d_tile_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict
     for (int idx = tid; idx < R * S; idx += NTHREADS)
         ws[idx] = load_weight(w, (long)c * R * S + (grad_input ? R * S - 1 - idx : idx), w_dtype);
     const T* xp = x + plane * xv.plane_stride;
+    // The forward's taps look back, so rows from m_end on feed no stored output and need not be in the input view (a
+    // row-range call stores no rows past its range); the input gradient looks forward, up to the plane's last row.
+    const int q_hi = grad_input ? H : m_end;
     for (int idx = tid; idx < th * tw; idx += NTHREADS) {
         const int rr = idx / tw, cc = idx - rr * tw;
         const int qq = m0 - pad_h + rr, kk = n0 - pad_w + cc;
         float v = 0.0f;
-        if (qq >= 0 && qq < H && kk >= 0 && kk < W && (!causal || kk <= qq))
+        if (qq >= 0 && qq < q_hi && kk >= 0 && kk < W && (!causal || kk <= qq))
             v = to_f32<T>(xp[(long)(qq - xv.row0) * xv.width + kk]);
         xs[idx] = v;
     }

@@ -32,8 +32,6 @@
 // an issuer's block range (the neighbouring issuer covers the other half).  For i = 0 an issuer first issues, with
 // accumulate = 0, k-steps that touch each of its blocks exactly once, then the others.  Measured: at M = 128 a
 // tcgen05.mma costs ~44 cycles for any N <= 64, which is why the schedule minimises the MMA count, not the MACs.
-#include <cstdlib>
-
 #include "kernels.cuh"
 #include "tc05.cuh"
 
@@ -45,28 +43,6 @@ int make_tensor_map_chunked(CUtensorMap* out, const void* base, uint64_t planes,
 namespace {
 using namespace tc05;
 
-// Per-role cycle counters of CTA 0 (where each role waits and works), compiled in only with -DMTA_CONV_PROFILE and
-// printed by the launcher when the environment variable MTA_CONV_PROFILE is set.
-#ifdef MTA_CONV_PROFILE
-__device__ long long g_prof[32];
-#define PROF_START long long prof_t = clock64();
-#define PROF_DECL long long prof_loc[4] = {0, 0, 0, 0};
-#define PROF_ACC(slot, cond)                        \
-    {                                               \
-        const long long prof_n = clock64();         \
-        prof_loc[(slot) & 3] += prof_n - prof_t;    \
-        prof_t = prof_n;                            \
-    }
-#define PROF_FLUSH(base, cond)                                                          \
-    if (blockIdx.x == 0 && lane == 0 && (cond))                                         \
-        for (int pi = 0; pi < 4; ++pi) g_prof[(base) + pi] = prof_loc[pi];
-#else
-#define PROF_START
-#define PROF_DECL
-#define PROF_ACC(slot, cond)
-#define PROF_FLUSH(base, cond)
-#endif
-
 constexpr int TM = 128;            // output rows per tile = MMA M
 constexpr int TN = 128;            // output columns per tile
 constexpr int NB = TN / 16;        // 16-column blocks
@@ -76,10 +52,7 @@ constexpr int NBOX = 2;            // 64-column TMA boxes per staged tile (128-b
                                    // (32-byte swizzle) holds the last k-step
 constexpr int NSTAGE = 3;
 constexpr int OUT_BYTES = 2 * TM * 128;   // output staging: two 64-column boxes of 128 rows x 128 bytes, 128-byte swizzle
-#ifndef MTA_CONV_NISS
-#define MTA_CONV_NISS 2
-#endif
-constexpr int NISS = MTA_CONV_NISS;   // MMA-issuing threads (warps 1, 8): 1 or 2
+constexpr int NISS = 2;               // MMA-issuing threads (warps 1, 8)
 constexpr int ZERO_WARP = 9;          // the warp that stores the zero tiles above the diagonal
 // First 16-column output block of issuer k (two issuers: blocks 0-3 and 4-7).
 __host__ __device__ constexpr int issuer_block0(int k) { return NISS == 1 ? (k == 0 ? 0 : NB) : (k == 0 ? 0 : k == 1 ? 4 : NB); }
@@ -250,14 +223,11 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            PROF_DECL
             TileIter it;
             it.init(g, t_begin);
             for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
                 const int st = n % NSTAGE;
-                PROF_START
                 mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
-                PROF_ACC(0, true)
                 uint8_t* xa = stage_base + st * stage_bytes;
                 mbar_expect_tx(&full_bar[st], (uint32_t)(NBOX * TH * 128 + TH * 32));
 #pragma unroll
@@ -267,7 +237,6 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 tma_load_3d(xa + NBOX * box_bytes, &mx3, &full_bar[st], it.n0() - pad8 + 128, it.m0(g) - g.lead - g.x_row0, it.plane);
                 *reinterpret_cast<volatile int*>(&tiles_loaded) = n + 1;
             }
-            PROF_FLUSH(12, true)
         }
     } else if (warp == ZERO_WARP) {
         // ---------------- zero tiles ----------------
@@ -318,14 +287,10 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         // the result (measured at B8 H16 S4096, 6 x 11: one issuer 1.19 ms, two 0.94 ms, three 1.01 ms; the tensor pipe
         // takes ~49 cycles per MMA, a single thread issues one per ~76).  The schedule of an issuer is compile-time (issue_tile<ISSUER>): every descriptor is the stage's
         // base descriptor plus a constant and a multiple of the row tap, all warp-uniform values.
-        PROF_DECL
         for (int n = 0; n < my_tiles; ++n) {
             const int st = n % NSTAGE, ab = n & 1;
-            PROF_START
             mbar_wait(&ready_bar[st], (n / NSTAGE) & 1, err_flag);
-            PROF_ACC(1, true)
             mbar_wait(&acc_empty[ab], ((n >> 1) & 1) ^ 1, err_flag);
-            PROF_ACC(2, true)
             fence_after_sync();
             if (lane == 0) {
                 const uint32_t xa_addr = smem_u32(stage_base + st * stage_bytes);
@@ -336,9 +301,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 mma_commit(&acc_full[ab]);
             }
             __syncwarp();
-            PROF_ACC(3, true)
         }
-        PROF_FLUSH(0, warp == 1)
     } else if (warp == 8 || warp == 9) {
         // issuer warp that this build does not use
     } else if (warp < 4 || warp >= 14) {
@@ -347,7 +310,6 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
         TileIter it;
         it.init(g, t_begin);
         int ph0 = -1, ph1 = -1, ph2 = -1;                 // head whose Toeplitz slices each stage holds (NSTAGE == 3)
-        PROF_DECL
         for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
             const int st = n % NSTAGE;
             const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
@@ -355,9 +317,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             uint8_t* xa = stage_base + st * stage_bytes;
             uint8_t* tb = xa + tb_off;
             // the stage (and its Toeplitz slices) is free once the MMAs of tile n - NSTAGE are done
-            PROF_START
             mbar_wait(&empty_bar[st], ((n / NSTAGE) & 1) ^ 1, err_flag);
-            PROF_ACC(4, warp == 2)
             int ph;
             if (st == 0) { ph = ph0; ph0 = head; }
             else if (st == 1) { ph = ph1; ph1 = head; }
@@ -379,9 +339,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                     if (g.split_w) *reinterpret_cast<T*>(tb + R * 1024 + off) = from_f32<T>(wv - to_f32<T>(hi));
                 }
             }
-            PROF_ACC(5, warp == 2)
             mbar_wait(&full_bar[st], (n / NSTAGE) & 1, err_flag);
-            PROF_ACC(6, warp == 2)
             // staged row sr is query m0-(R-1)+sr; staged column sc is key n0-pad8+sc, in box sc/64 at byte
             // sr*128 + (((sc%64)/8) ^ (sr%8))*16 + (sc%8)*2.  Zero the keys above the query.
             if (g.causal && n0 - pad8 + NCH * 8 - 1 > m0 - g.lead) {
@@ -411,16 +369,13 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             fence_proxy_async();          // generic-proxy writes above must be visible to the MMAs (async proxy)
             __syncwarp();
             if (lane == 0) mbar_arrive(&ready_bar[st]);
-            PROF_ACC(7, warp == 2)
         }
-        PROF_FLUSH(4, warp == 2)
     } else {
         // ---------------- epilogue: warps 4-7 drain columns 0..63, warps 10-13 columns 64..127 ----------------
         const int quarter = warp & 3;                        // the TMEM lanes a warp may read depend on its index mod 4
         const int half = warp >= 10 ? 1 : 0;
         const bool issuer = (warp == 4 && lane == 0);
         const int row = quarter * 32 + lane;                 // row of the tile this thread owns
-        PROF_DECL
         TileIter it;
         it.init(g, t_begin);
         for (int n = 0; n < my_tiles; ++n, it.next(g, g.tiles_m)) {
@@ -428,14 +383,11 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             const int plane = it.plane, m0 = it.m0(g), n0 = it.n0();
             uint8_t* obuf = out_base + ab * OUT_BYTES;       // staging tile n % 2: two 64-column boxes
             uint8_t* orow = obuf + half * (TM * 128) + row * 128;
-            PROF_START
             mbar_wait(&acc_full[ab], (n >> 1) & 1, err_flag);
             __syncwarp();
             fence_after_sync();
-            PROF_ACC(8, warp == 4)
             if (issuer) bulk_wait_read_1();                  // the store of tile n-2 has finished reading this staging tile
             named_barrier(1, 256);
-            PROF_ACC(9, warp == 4)
             const int q = m0 + row;
 #pragma unroll
             for (int cblk = 0; cblk < 2; ++cblk) {
@@ -465,7 +417,6 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[ab]);
-            PROF_ACC(10, warp == 4)
             fence_proxy_async();                             // staging tile written through the generic proxy, read by TMA
             named_barrier(1, 256);
             if (issuer) {
@@ -474,9 +425,7 @@ conv2d_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant
                 if (n0 + 64 < g.W) tma_store_3d(&my, obuf + TM * 128, n0 + 64, m0 - y_row0, plane);
                 bulk_commit();
             }
-            PROF_ACC(11, warp == 4)
         }
-        PROF_FLUSH(8, warp == 4)
         if (issuer) bulk_wait_all();
     }
     fence_before_sync();
@@ -538,19 +487,6 @@ int launch_tc05(const void* x, PlaneView xv, long x_rows_stored, const void* w, 
     const unsigned grid = (unsigned)std::min<long>(g.total_tiles, sms);
     conv2d_tc05_kernel<T><<<grid, THREADS, smem, st>>>(mx, mx3, my, w, w_dtype, yv.row0, g, flag);
     MTA_LAUNCH_OK("conv2d_tc05_kernel");
-#ifdef MTA_CONV_PROFILE
-    if (getenv("MTA_CONV_PROFILE")) {
-        cudaDeviceSynchronize();
-        long long h[32], z[32] = {};
-        cudaMemcpyFromSymbol(h, g_prof, sizeof(h));
-        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
-        const long n0 = (g.total_tiles + grid - 1) / grid;
-        fprintf(stderr, "conv2d_tc05 clk/tile (CTA 0, %ld tiles): producer wait_empty %lld | mma wait_ready %lld wait_acc %lld issue %lld | "
-                "fixup wait_free %lld toeplitz %lld wait_full %lld zeroing %lld | epilogue wait_acc %lld wait_store %lld drain %lld store %lld\n",
-                n0, h[12] / n0, h[1] / n0, h[2] / n0, h[3] / n0, h[4] / n0, h[5] / n0, h[6] / n0, h[7] / n0, h[8] / n0, h[9] / n0,
-                h[10] / n0, h[11] / n0);
-    }
-#endif
     return MTA_OK;
 }
 

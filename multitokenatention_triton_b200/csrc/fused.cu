@@ -16,24 +16,18 @@ namespace {
 struct Plan {
     int ra, rb, r0, r1;      // first score row, first softmax row, first and one-past-last output row
     size_t buf_bytes;        // one scratch buffer
-    size_t stats_bytes;      // row statistics of the logits: (max, sum) per (batch, head, row)
-    size_t table_bytes[2];   // Toeplitz fragment tables of the two convs (fused conv + mix path)
-    size_t total() const { return 2 * buf_bytes + stats_bytes + table_bytes[0] + table_bytes[1]; }
+    size_t total() const { return 2 * buf_bytes; }
 };
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 Plan make_plan(int B, int H, int S, int cq, int cq2, int r0, int r1, int dtype) {
-    // tables are sized for float32 weights (two terms) so the size does not depend on the weight dtype
     Plan p;
     p.r0 = r0;
     p.r1 = r1;
     p.rb = r0 - (cq2 - 1) > 0 ? r0 - (cq2 - 1) : 0;
     p.ra = p.rb - (cq - 1) > 0 ? p.rb - (cq - 1) : 0;
     p.buf_bytes = round_up((size_t)B * H * (size_t)(r1 - p.ra) * S * dtype_size(dtype), 256);
-    p.stats_bytes = round_up((size_t)B * H * (size_t)(r1 - p.rb) * 8, 256);
-    p.table_bytes[0] = round_up(conv_mix_table_bytes(H, cq, MTA_F32), 256);
-    p.table_bytes[1] = round_up(conv_mix_table_bytes(H, cq2, MTA_F32), 256);
     return p;
 }
 
@@ -116,9 +110,6 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     char* ws = static_cast<char*>(workspace);
     void* bufA = ws;
     void* bufB = ws + pl.buf_bytes;
-    void* stats = ws + 2 * pl.buf_bytes;
-    void* table1 = ws + 2 * pl.buf_bytes + pl.stats_bytes;
-    void* table2 = ws + 2 * pl.buf_bytes + pl.stats_bytes + pl.table_bytes[0];
     const PlaneView pv{(long)(pl.r1 - pl.ra) * S, pl.ra, S};
     const long planes = (long)B * H;
     const float scale = 1.0f / sqrtf((float)D);
@@ -135,27 +126,6 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     } else {
     if ((rc = trace_mark("qk_scores", st))) return rc;
     if ((rc = qk_scores_launch(q, k, bufA, pv, B, H, S, D, scale, round16, causal, pl.ra, pl.r1, dtype, st))) return rc;
-    }
-    // mta_set_variant("fused", 2): two fused "conv + head mix" launches with the softmax folded into them.  Measured at
-    // B8 H16 S4096: 12.1 ms per forward against 7.8 ms for the stage-by-stage pipeline below - both the conv and the
-    // mix run on the legacy mma.sync pipes, which a single CTA keeps less busy than several independent kernels do -
-    // so it is not the default.
-    if (variant("fused") == 2 && conv_mix_supported(H, S, cq, ck, causal, dtype, w_dtype, bufA, bufB) &&
-        conv_mix_supported(H, S, cq2, ck2, causal, dtype, w_dtype, bufA, bufB)) {
-        const long nrows = pl.r1 - pl.ra;
-        if ((rc = trace_mark("conv1+head_mix1", st))) return rc;
-        if ((rc = conv_mix_prepare(w1, w_dtype, H, cq, ck, dtype, table1, st))) return rc;
-        if ((rc = conv_mix_prepare(w2, w_dtype, H, cq2, ck2, dtype, table2, st))) return rc;
-        if ((rc = conv_mix_launch(bufA, pv, nrows, table1, W1, w_dtype, bufB, pv, B, H, S, cq, ck, pl.rb, pl.r1, nullptr, stats,
-                                  pl.rb, pl.r1 - pl.rb, dtype, st)))
-            return rc;
-        if ((rc = trace_mark("softmax+conv2+head_mix2", st))) return rc;
-        if ((rc = conv_mix_launch(bufB, pv, nrows, table2, W2, w_dtype, bufA, pv, B, H, S, cq2, ck2, pl.r0, pl.r1, stats, nullptr,
-                                  pl.rb, pl.r1 - pl.rb, dtype, st)))
-            return rc;
-        if ((rc = trace_mark("pv", st))) return rc;
-        if ((rc = pv_launch(bufA, pv, nrows, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st))) return rc;
-        return trace_end(st);
     }
     if (!qk_in_conv) {
         if ((rc = trace_mark("conv1", st))) return rc;
@@ -180,7 +150,7 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     return trace_end(st);
 }
 
-// One kernel, no scratch: 16-bit dtypes the fused kernel takes (mta_set_variant("fused", 4) keeps the three-launch path).
+// One kernel, no scratch: 16-bit dtypes the fused kernel takes (mta_set_variant("fused", 2) keeps the three-launch path).
 static bool conv_attn_one_kernel(int S, int D, int cq, int ck, int causal, int dtype, int w_dtype) {
     return variant("fused") == 0 && variant("gemm") == 0 && variant("conv2d") == 0 &&
            conv_attn_fused_shape_ok(S, D, cq, ck, causal, dtype, w_dtype);
@@ -220,7 +190,7 @@ int mta_conv_attn_fwd(const void* q, const void* k, const void* v, const void* w
     const long planes = (long)B * H;
     int rc;
     // 16-bit dtypes: the raw scores are computed inside the conv's kernel (scale 1: the conv attention scales after its conv)
-    if ((variant("fused") == 0 || variant("fused") == 4) && variant("gemm") == 0 && variant("conv2d") == 0 && planes <= 65535 &&
+    if ((variant("fused") == 0 || variant("fused") == 2) && variant("gemm") == 0 && variant("conv2d") == 0 && planes <= 65535 &&
         qk_conv_supported(q, k, bufB, pv, S, D, cq, ck, causal, dtype, w_dtype)) {
         if ((rc = qk_conv_launch(q, k, w, w_dtype, bufB, pv, B, H, S, D, cq, ck, 1.0f, 0, S, dtype, st))) return rc;
     } else {

@@ -1,7 +1,6 @@
 // Chooses the implementation of the two contractions of the forward: tcgen05 tensor cores for 16-bit
 // dtypes with D in {64,128} and 16-byte aligned rows, CUDA cores otherwise.  mta_set_variant("gemm", 1)
-// forces the CUDA-core kernels, ("gemm", 2) requires the tensor-core ones, ("gemm", 3) selects the one-CTA-per-tile
-// version of the score kernel.
+// forces the CUDA-core kernels, ("gemm", 2) requires the tensor-core ones.
 #include "kernels.cuh"
 
 namespace mta {
@@ -12,8 +11,6 @@ int qk_scores_launch(const void* q, const void* k, void* s, PlaneView sv, int B,
     const int want = variant("gemm");
     const bool ok = tc05_contractions_supported(S, D, dtype, q, k, s, sv);
     MTA_REQUIRE(want != 2 || ok, "qk_scores: the tensor-core variant needs a 16-bit dtype, D in {64,128}, S %% 8 == 0 and 16-byte aligned tensors");
-    if (ok && want == 3)     // one CTA per tile (kept for comparison; latency-bound)
-        return qk_scores_tc05_launch(q, k, s, sv, B, H, S, D, scale, round_scale, causal, row_begin, row_end, dtype, st);
     if (ok && want != 1)
         return qk_persistent_launch(q, k, s, sv, B, H, S, D, 1, scale, round_scale, causal, 0, 1, 0, row_begin, row_end, dtype, st);
     return qk_scores_simt_launch(q, k, s, sv, B, H, S, D, scale, round_scale, causal, row_begin, row_end, dtype, st);

@@ -1,9 +1,9 @@
 // The two contractions of the forward on the 5th-generation tensor cores (tcgen05), 16-bit dtypes:
-//   scores tile  S[128 q x 128 k] = Q[128 x D] K[128 x D]^T   (both operands K-major, D in {64,128})
 //   output tile  O[128 q x D]     = sum over key tiles  P[128 q x 128 k] V[128 k x D]   (A K-major, B MN-major)
 // Operand tiles arrive by TMA (128-byte swizzle, out-of-range rows and columns read as zero), the
 // accumulator lives in tensor memory, and only tiles that touch keys k <= q are visited when causal.
 // They stand in for the torch.matmul calls at mta_attention_triton.py:68-71 and :89.
+#include <cstddef>
 #include <mutex>
 
 #include "kernels.cuh"
@@ -13,7 +13,17 @@ namespace mta {
 
 // ---- host helpers ----------------------------------------------------------------------------------
 namespace {
-__device__ int g_wait_timeout = 0;
+// What a bounded wait raises when it gives up: the flag the kernels test on entry, and the address of its mirror in
+// page-locked host memory, which lets the entry points see a timeout without synchronising with the device.
+struct WaitFlag {
+    int flag;
+    int pad;
+    int* host_mirror;
+};
+__device__ WaitFlag g_wait_timeout = {0, 0, nullptr};
+std::mutex g_flag_mutex;
+int* g_flag_dev[64] = {};          // per device: address of g_wait_timeout.flag
+int* g_flag_host[64] = {};         // per device: the host mirror (mapped page-locked memory)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -34,16 +44,47 @@ EncodeTiledFn encode_fn() {
 }  // namespace
 
 int wait_flag_ptr(int** out) {
-    static int* ptrs[64] = {};
     int dev = 0;
     MTA_CUDA_OK(cudaGetDevice(&dev));
     MTA_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
-    if (!ptrs[dev]) {
+    std::lock_guard<std::mutex> lock(g_flag_mutex);
+    if (!g_flag_dev[dev]) {
+        // first tcgen05 launch on this device: look up the flag and give it a host-visible mirror (4 bytes of mapped
+        // page-locked memory, kept until the process ends)
         void* p = nullptr;
         MTA_CUDA_OK(cudaGetSymbolAddress(&p, g_wait_timeout));
-        ptrs[dev] = static_cast<int*>(p);
+        int* host = nullptr;
+        int* host_dev = nullptr;
+        MTA_CUDA_OK(cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped));
+        *host = 0;
+        MTA_CUDA_OK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&host_dev), host, 0));
+        MTA_CUDA_OK(cudaMemcpy(static_cast<char*>(p) + offsetof(WaitFlag, host_mirror), &host_dev, sizeof(host_dev), cudaMemcpyHostToDevice));
+        g_flag_host[dev] = host;
+        g_flag_dev[dev] = static_cast<int*>(p);
     }
-    *out = ptrs[dev];
+    *out = g_flag_dev[dev];
+    return MTA_OK;
+}
+
+// True when a bounded wait has given up on the current device since the last mta_device_status (no synchronisation:
+// reads the host mirror the kernel wrote).
+bool wait_flag_raised() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    const int* host = g_flag_host[dev];
+    return host && *reinterpret_cast<const volatile int*>(host) != 0;
+}
+
+// Raises the flag from the host as a kernel's timed-out wait would (fault injection without a fault on the device).
+int wait_flag_inject(cudaStream_t st) {
+    int* flag = nullptr;
+    if (int rc = wait_flag_ptr(&flag)) return rc;
+    int dev = 0;
+    MTA_CUDA_OK(cudaGetDevice(&dev));
+    const int one = 1;
+    MTA_CUDA_OK(cudaMemcpyAsync(flag, &one, sizeof(int), cudaMemcpyHostToDevice, st));
+    MTA_CUDA_OK(cudaStreamSynchronize(st));
+    *reinterpret_cast<volatile int*>(g_flag_host[dev]) = 1;
     return MTA_OK;
 }
 
@@ -135,137 +176,10 @@ __device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
     return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
 }
 
-// Number of key tiles that query tile tq reaches: ceil(last query row + 1 / TILE), clamped.
-__device__ __forceinline__ int key_tiles_for(int tq, int row_begin, int row_end, int S, int causal) {
-    const int all = (S + TILE - 1) / TILE;
-    if (!causal) return all;
-    const int q_last = min(row_begin + (tq + 1) * TILE, row_end);     // one past the last row of the tile
-    return min((q_last + TILE - 1) / TILE, all);
-}
-
-// ------------------------------------------------------------------------------------------------
-// One CTA (4 warps) per 128 x 128 score tile.  Thread 0 issues the TMA loads and the MMAs; all four warps
-// drain the accumulator: warp w owns TMEM lanes 32w..32w+31 = tile rows, each lane one row.  The tile leaves
-// through shared memory and a TMA tiled store.
-template <typename T, int D>
-__global__ void __launch_bounds__(128)
-qk_scores_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                      const __grid_constant__ CUtensorMap ms, int s_row0, int S, float scale, int round_scale, int causal,
-                      int row_begin, int row_end, int* err_flag) {
-    constexpr int NBOX = D / 64;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = align_1024(smem_raw);
-    uint8_t* sq = smem;
-    uint8_t* sk = smem + NBOX * BOX_BYTES;
-    __shared__ __align__(8) uint64_t full_bar, mma_bar;
-    __shared__ uint32_t tmem_slot;
-
-    __shared__ int abort_flag;      // an earlier bounded wait on this device gave up: the whole CTA does nothing
-    if (threadIdx.x == 0) abort_flag = *reinterpret_cast<volatile int*>(err_flag);
-    __syncthreads();
-    if (abort_flag != 0) return;
-    // linear tile index -> (query tile, key tile)
-    int tq = 0, tk = (int)blockIdx.x;
-    for (;; ++tq) {
-        const int nk = key_tiles_for(tq, row_begin, row_end, S, causal);
-        if (tk < nk) break;
-        tk -= nk;
-    }
-    const int bh = (int)blockIdx.y;
-    const int q0 = row_begin + tq * TILE, k0 = tk * TILE;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            mbar_init(&full_bar, 1);
-            mbar_init(&mma_bar, 1);
-            fence_mbar_init();
-            prefetch_tensormap(&mq);
-            prefetch_tensormap(&mk);
-            prefetch_tensormap(&ms);
-        }
-        __syncwarp();
-        tmem_alloc(&tmem_slot, 128);
-    }
-    fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
-    const uint32_t tmem = tmem_slot;
-
-    if (threadIdx.x == 0) {
-        mbar_expect_tx(&full_bar, 2 * NBOX * BOX_BYTES);
-#pragma unroll
-        for (int j = 0; j < NBOX; ++j) {
-            tma_load_3d(sq + j * BOX_BYTES, &mq, &full_bar, j * 64, q0, bh);
-            tma_load_3d(sk + j * BOX_BYTES, &mk, &full_bar, j * 64, k0, bh);
-        }
-        mbar_wait(&full_bar, 0, err_flag);
-        fence_after_sync();
-        constexpr uint32_t idesc = instr_desc_f16(AbFormat<T>::value, 0, 0, TILE, TILE);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t off = (kk / 4) * BOX_BYTES + (kk % 4) * 32;
-            mma_f16_ss(tmem, smem_desc_sw128(smem_u32(sq) + off, 16, 1024), smem_desc_sw128(smem_u32(sk) + off, 16, 1024),
-                       idesc, kk > 0);
-        }
-        mma_commit(&mma_bar);
-    }
-    __syncwarp();
-    mbar_wait(&mma_bar, 0, err_flag);
-    __syncwarp();
-    fence_after_sync();
-
-    // Epilogue: a thread owns one row of the tile, so the 16-bit tile is staged in shared memory (over the operand
-    // tiles, which are dead now) in the 128-byte-swizzled layout and leaves as two TMA tiled stores.
-    const int row = warp * 32 + lane;
-    const int q = q0 + row;
-    const float sc = round_scale ? round_to<T>(scale) : scale;
-    uint8_t* orow = smem + row * 128;
-#pragma unroll 1
-    for (int c = 0; c < TILE / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int v8 = 0; v8 < 4; ++v8) {
-            const int col = c * 32 + v8 * 8;
-            const int k = k0 + col;
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float a = __uint_as_float(r[v8 * 8 + e]);
-                f[e] = round_scale ? round_to<T>(a) * sc : a * sc;
-                if (causal && k + e > q) f[e] = 0.0f;        // above the diagonal inside a visited tile: written as 0
-            }
-            uint4 o;
-            o.x = pack2<T>(f[0], f[1]);
-            o.y = pack2<T>(f[2], f[3]);
-            o.z = pack2<T>(f[4], f[5]);
-            o.w = pack2<T>(f[6], f[7]);
-            const int ch = (col & 63) >> 3;
-            *reinterpret_cast<uint4*>(orow + (col >> 6) * BOX_BYTES + ((ch ^ (row & 7)) << 4)) = o;
-        }
-    }
-    fence_proxy_async();
-    fence_before_sync();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        // rows past row_end and columns past S are outside the tensor map and are clipped
-        tma_store_3d(&ms, smem, k0, q0 - s_row0, bh);
-        if (k0 + 64 < S) tma_store_3d(&ms, smem + BOX_BYTES, k0 + 64, q0 - s_row0, bh);
-        bulk_commit();
-        bulk_wait_read();
-    }
-    if (warp == 0) tmem_dealloc(tmem, 128);
-}
-
 // ------------------------------------------------------------------------------------------------
 // O tile = sum over key tiles of P tile x V tile.  Warp 0: TMA producer; warp 1: zeroes the part of a
 // diagonal P tile that lies above the diagonal, then issues the MMAs; warps 2..5: epilogue.
-#ifndef MTA_PV_STAGES
-#define MTA_PV_STAGES 3
-#endif
-constexpr int PV_STAGES = MTA_PV_STAGES;
+constexpr int PV_STAGES = 3;
 constexpr int PV_THREADS = 192;
 constexpr int PV_KEYS = 64;               // keys per pipeline stage: 32 KB stages, so two CTAs fit on an SM and one CTA's
                                           // start-up and epilogue overlap the other's steady state
@@ -400,33 +314,6 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
 }
 
 template <typename T, int D>
-int launch_qk(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, float scale, int round_scale,
-              int causal, int row_begin, int row_end, cudaStream_t st) {
-    CUtensorMap mq, mk;
-    int rc;
-    if ((rc = make_tensor_map_3d(&mq, q, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
-    if ((rc = make_tensor_map_3d(&mk, k, (uint64_t)B * H, S, D, D, (uint64_t)S * D, 64, TILE, true))) return rc;
-    CUtensorMap ms;      // rows past row_end are outside this map, so a tile's store never touches them
-    if ((rc = make_tensor_map_3d(&ms, s, (uint64_t)B * H, (uint64_t)(row_end - sv.row0), S, S, (uint64_t)sv.plane_stride, 64, TILE, true)))
-        return rc;
-    int* flag = nullptr;
-    if ((rc = wait_flag_ptr(&flag))) return rc;
-    const int n_qt = (row_end - row_begin + TILE - 1) / TILE, all_k = (S + TILE - 1) / TILE;
-    long tiles = 0;
-    for (int tq = 0; tq < n_qt; ++tq) {
-        const int q_last = std::min(row_begin + (tq + 1) * TILE, row_end);
-        tiles += causal ? std::min((q_last + TILE - 1) / TILE, all_k) : all_k;
-    }
-    const size_t smem = 2 * (D / 64) * BOX_BYTES + 1024;
-    MTA_CUDA_OK(cudaFuncSetAttribute(qk_scores_tc05_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((unsigned)tiles, (unsigned)(B * H));
-    qk_scores_tc05_kernel<T, D><<<grid, 128, smem, st>>>(mq, mk, ms, sv.row0, S, scale, round_scale, causal, row_begin,
-                                                         row_end, flag);
-    MTA_LAUNCH_OK("qk_scores_tc05_kernel");
-    return MTA_OK;
-}
-
-template <typename T, int D>
 int launch_pv(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int causal, int row_begin,
               int row_end, long p_rows_stored, cudaStream_t st) {
     CUtensorMap mp, mv;
@@ -452,15 +339,6 @@ bool tc05_contractions_supported(int S, int D, int dtype, const void* a, const v
            aligned16(a) && aligned16(b) && aligned16(c);
 }
 
-int qk_scores_tc05_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
-                          int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st) {
-#define MTA_QK(TT, DD) return launch_qk<TT, DD>(q, k, s, sv, B, H, S, scale, round_scale, causal, row_begin, row_end, st)
-    if (dtype == MTA_BF16) { if (D == 64) MTA_QK(__nv_bfloat16, 64); MTA_QK(__nv_bfloat16, 128); }
-    if (D == 64) MTA_QK(__half, 64);
-    MTA_QK(__half, 128);
-#undef MTA_QK
-}
-
 int pv_tc05_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
                    int causal, int row_begin, int row_end, int dtype, cudaStream_t st) {
 #define MTA_PV(TT, DD) return launch_pv<TT, DD>(p, pview, v, o, B, H, S, causal, row_begin, row_end, p_rows_stored, st)
@@ -477,10 +355,14 @@ int device_wait_status(cudaStream_t st, int* timed_out) {
     int h = 0;
     MTA_CUDA_OK(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
     MTA_CUDA_OK(cudaStreamSynchronize(st));
-    if (h) {
+    int dev = 0;
+    MTA_CUDA_OK(cudaGetDevice(&dev));
+    if (h || *reinterpret_cast<volatile int*>(g_flag_host[dev])) {
         int zero = 0;
         MTA_CUDA_OK(cudaMemcpyAsync(flag, &zero, sizeof(int), cudaMemcpyHostToDevice, st));
         MTA_CUDA_OK(cudaStreamSynchronize(st));
+        *reinterpret_cast<volatile int*>(g_flag_host[dev]) = 0;
+        h = 1;
     }
     *timed_out = h;
     return MTA_OK;

@@ -130,10 +130,8 @@ constexpr int MMA_KEYS_PER_WARP = 64;       // keys of one row handled per warp 
 // CP = padded head count (8, 16 or 32).  KSTEPS = CP/8 MMA k-steps, MT = number of 16-row output tiles.
 // SPLITW: the weight is float32 and is fed as two TF32 terms (high part + remainder), which keeps ~21 of
 // its mantissa bits; 16-bit weights are exact in TF32 and need one term.
-#ifndef MTA_HL_MIN_CTAS_WIDE
-#define MTA_HL_MIN_CTAS_WIDE 3     // resident CTAs per SM asked for when there are more than 16 heads (B1 H32 S8192 bf16:
-                                   // 1.015 ms unconstrained at 182 registers, 0.891 with 3, 1.869 with 4, which spills)
-#endif
+constexpr int HL_MIN_CTAS_WIDE = 3;    // resident CTAs per SM asked for when there are more than 16 heads (B1 H32 S8192 bf16:
+                                       // 1.015 ms unconstrained at 182 registers, 0.891 with 3, 1.869 with 4, which spills)
 // The kernel body; the two __global__ entry points below differ only in their register bound.
 template <typename T, int CP, bool SPLITW>
 __device__ __forceinline__ void
@@ -299,9 +297,9 @@ head_linear_mma_kernel(const T* __restrict__ x, PlaneView xv, const void* __rest
     head_linear_mma_body<T, CP, SPLITW>(x, xv, Wm, w_dtype, y, yv, C, Q, causal, fill, row_begin, row_end, rows_per_cta,
                                         write_upper, w_transposed);
 }
-// More than 16 heads: twice the accumulators and weight fragments; bounded so that MTA_HL_MIN_CTAS_WIDE CTAs stay resident.
+// More than 16 heads: twice the accumulators and weight fragments; bounded so that HL_MIN_CTAS_WIDE CTAs stay resident.
 template <typename T, int CP, bool SPLITW>
-__global__ void __launch_bounds__(MMA_WARPS * 32, MTA_HL_MIN_CTAS_WIDE)
+__global__ void __launch_bounds__(MMA_WARPS * 32, HL_MIN_CTAS_WIDE)
 head_linear_mma_wide_kernel(const T* __restrict__ x, PlaneView xv, const void* __restrict__ Wm, int w_dtype,
                             T* __restrict__ y, PlaneView yv, int C, int Q, int causal, float fill, int row_begin,
                             int row_end, int rows_per_cta, int write_upper, int w_transposed) {
@@ -337,11 +335,8 @@ __device__ __forceinline__ void stat_merge(float& m, float& s, float m2, float s
     m = mn;
 }
 
-#ifndef MTA_MS_DEPTH
-#define MTA_MS_DEPTH 3             // ring slots per warp: loads run two 64-key blocks ahead (measured: 2 -> 1.371 ms,
+constexpr int MS_DEPTH = 3;        // ring slots per warp: loads run two 64-key blocks ahead (measured: 2 -> 1.371 ms,
                                    // 3 -> 1.359, 4 -> 1.387, 6 -> 1.455 for B8 H16 S4096 bf16)
-#endif
-constexpr int MS_DEPTH = MTA_MS_DEPTH;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid, uint64_t policy) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -374,17 +369,11 @@ template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float& l
     hi = f.y;
 }
 
-#ifndef MTA_MS_WARPS
-#define MTA_MS_WARPS 4             // warps of the CTA that owns a row
-#endif
-#ifndef MTA_MS_MIN_CTAS
-#define MTA_MS_MIN_CTAS 4          // resident CTAs per SM the register allocation aims at
-#endif
-#ifndef MTA_MS_MIN_CTAS_WIDE
-#define MTA_MS_MIN_CTAS_WIDE 3     // the same for more than 16 heads: twice the accumulators and weight fragments spill at
-                                   // 128 registers (B1 H32 S8192 bf16: 2.38 ms with 4, 1.67 with 3, 1.73 with 2)
-#endif
-constexpr int ms_min_ctas(int cp) { return cp > 16 ? MTA_MS_MIN_CTAS_WIDE : MTA_MS_MIN_CTAS; }
+constexpr int MS_WARPS = 4;            // warps of the CTA that owns a row
+constexpr int MS_MIN_CTAS = 4;         // resident CTAs per SM the register allocation aims at
+constexpr int MS_MIN_CTAS_WIDE = 3;    // the same for more than 16 heads: twice the accumulators and weight fragments spill at
+                                       // 128 registers (B1 H32 S8192 bf16: 2.38 ms with 4, 1.67 with 3, 1.73 with 2)
+constexpr int ms_min_ctas(int cp) { return cp > 16 ? MS_MIN_CTAS_WIDE : MS_MIN_CTAS; }
 
 template <typename T, int CP, bool SPLITW, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, ms_min_ctas(CP))
@@ -687,7 +676,7 @@ head_mix_softmax_kernel(const T* __restrict__ x, PlaneView xv, const void* __res
 template <typename T, int CP>
 int launch_mix_softmax(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C, int Q,
                        int row_begin, int row_end, bool write_upper, cudaStream_t st) {
-    constexpr int WARPS = MTA_MS_WARPS;
+    constexpr int WARPS = MS_WARPS;
     dim3 grid((unsigned)(row_end - row_begin), (unsigned)N);
     const size_t smem = (size_t)WARPS * MS_DEPTH * (CP / 4) * 32 * sizeof(uint4);
     constexpr size_t stat_smem = 2 * sizeof(float) * WARPS * 16 * ((CP + 15) / 16);   // the kernel's static arrays count too

@@ -60,14 +60,6 @@ int qk_scores_simt_launch(const void* q, const void* k, void* s, PlaneView sv, i
 int pv_simt_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
                    int row_begin, int row_end, int dtype, cudaStream_t st);
 
-// Fused conv + head mix stage (conv_mix.cu): 16-bit dtypes, causal, C <= 16 heads, S <= 17, W a multiple of 8.
-bool conv_mix_supported(int C, int W, int R, int S, int causal, int dtype, int w_dtype, const void* x, const void* y);
-size_t conv_mix_table_bytes(int C, int R, int w_dtype);
-int conv_mix_prepare(const void* w, int w_dtype, int C, int R, int S, int dtype, void* table, cudaStream_t st);
-int conv_mix_launch(const void* x, PlaneView xv, long x_rows_stored, const void* table, const void* Wm, int w_dtype, void* y,
-                    PlaneView yv, int N, int C, int W, int R, int S, int row_begin, int row_end, const void* stats_in,
-                    void* stats_out, int stats_row0, int stats_rows, int dtype, cudaStream_t st);
-
 // tcgen05 version of the conv (conv2d_tc05.cu): 16-bit dtypes, S <= 17, W a multiple of 8, R small enough for its
 // shared-memory rings (R <= 13 with 16-bit weights).
 bool conv2d_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int W, int R, int S, int dtype,
@@ -80,8 +72,6 @@ int conv2d_tc05_launch(const void* x, PlaneView xv, long x_rows_stored, const vo
 
 // tcgen05 tensor-core versions (gemm_tc05.cu): 16-bit dtypes, D in {64,128}, S a multiple of 8.
 bool tc05_contractions_supported(int S, int D, int dtype, const void* a, const void* b, const void* c, PlaneView view);
-int qk_scores_tc05_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
-                          int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 int pv_tc05_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
                    int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 // Persistent, warp-specialised score-tile kernel (qk_persistent.cu); same domain as the kernels above.
@@ -106,5 +96,10 @@ int conv_attn_fused_launch(const void* q, const void* k, const void* v, const vo
                            int R, int KS, float score_scale, float sm_scale, int row_begin, int row_end, int dtype, cudaStream_t st);
 // Reads and clears the flag raised by a device-side bounded wait that gave up (synchronises `st`).
 int device_wait_status(cudaStream_t st, int* timed_out);
+// True when such a wait has given up on the current device since the last device_wait_status; reads the flag's mirror in
+// host memory, no synchronisation.
+bool wait_flag_raised();
+// Raises the flag from the host as a timed-out wait would.
+int wait_flag_inject(cudaStream_t st);
 
 }  // namespace mta

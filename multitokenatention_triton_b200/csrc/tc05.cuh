@@ -53,6 +53,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// A wait gave up: raise the device flag (later kernels return at once) and its mirror in host memory, whose address sits
+// two ints after the flag (the host then sees the timeout without synchronising).
+__device__ __forceinline__ void raise_wait_flag(int* err_flag) {
+    if (atomicExch(err_flag, 1) == 0) {
+        int* mirror = *reinterpret_cast<int* volatile*>(err_flag + 2);
+        if (mirror) {
+            *reinterpret_cast<volatile int*>(mirror) = 1;
+            __threadfence_system();
+        }
+    }
+}
 // Bounded wait for the phase with the given parity.  Returns false (and raises *err_flag) on timeout.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err_flag) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
@@ -62,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
         // once any wait on the device has given up, every other one gives up quickly
         if ((i & 1023u) == 1023u && *reinterpret_cast<volatile int*>(err_flag) != 0) return false;
     }
-    atomicExch(err_flag, 1);
+    raise_wait_flag(err_flag);
     return false;
 }
 
@@ -73,7 +84,7 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, i
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 8191u) == 8191u && *reinterpret_cast<volatile int*>(err_flag) != 0) return false;
     }
-    atomicExch(err_flag, 1);
+    raise_wait_flag(err_flag);
     return false;
 }
 
@@ -240,7 +251,8 @@ int make_tensor_map_3d_mode(CUtensorMap* out, const void* base, uint64_t planes,
                             uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_cols, uint32_t box_rows,
                             int swizzle_bytes);
 
-// Device address of the word that bounded waits raise on timeout (one per device, owned by the library).
+// Device address of the word that bounded waits raise on timeout (one per device, owned by the library; the first call
+// on a device also sets up the flag's mirror in page-locked host memory).
 int wait_flag_ptr(int** out);
 
 int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,

@@ -55,14 +55,17 @@ def test_bad_arguments_are_rejected_without_a_device():
 
 def test_workspace_size_formula():
     L = _lib.lib()
-    # two buffers of B*H*(rows incl. halo)*S elements, 256-byte rounded
-    # two score planes of B*H*(rows incl. halo)*S elements + row statistics (8 bytes per (b,h,row)) + two Toeplitz
-    # fragment tables (H * taps * 2 KiB each), every part rounded up to 256 bytes
+    # two score planes of B*H*(rows incl. halo)*S elements, each rounded up to 256 bytes
     n = L.mta_workspace_bytes(2, 4, 64, 32, 6, 11, 3, 3, 0, 64, 1)
-    assert n == 2 * 2 * 4 * 64 * 64 * 2 + 2 * 4 * 64 * 8 + 4 * 6 * 2048 + 4 * 3 * 2048
+    assert n == 2 * 2 * 4 * 64 * 64 * 2
     n = L.mta_workspace_bytes(2, 4, 64, 32, 6, 11, 3, 3, 32, 48, 0)
     r256 = lambda v: (v + 255) // 256 * 256
-    assert n == 2 * r256(2 * 4 * (48 - 32 + 7) * 64 * 4) + r256(2 * 4 * (48 - 32 + 2) * 8) + 4 * 6 * 2048 + 4 * 3 * 2048
+    assert n == 2 * r256(2 * 4 * (48 - 32 + 7) * 64 * 4)
+    # the conv attention: no scratch where the one-kernel path applies, two score planes otherwise
+    assert L.mta_conv_attn_workspace_bytes(2, 4, 512, 128, 6, 11, 1, 1, 1) == 0
+    assert L.mta_conv_attn_workspace_bytes(2, 4, 512, 128, 6, 11, 1, 0, 0) == 2 * 2 * 4 * 512 * 512 * 4      # float32
+    assert L.mta_conv_attn_workspace_bytes(2, 4, 512, 128, 6, 11, 0, 1, 1) == 2 * 2 * 4 * 512 * 512 * 2      # not causal
+    assert L.mta_conv_attn_workspace_bytes(2, 4, 512, 128, 6, 19, 1, 1, 1) == 2 * 2 * 4 * 512 * 512 * 2      # 19 taps wide
     assert L.mta_workspace_bytes(2, 4, 64, 32, 6, 11, 3, 3, 32, 70, 0) == 0
     assert L.mta_set_variant(b"nope", 1) == 1 and L.mta_set_variant(b"conv2d", 0) == 0
 

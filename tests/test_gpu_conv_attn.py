@@ -54,12 +54,13 @@ def test_one_kernel_conv_attention_against_the_oracle(name):
 def test_one_kernel_agrees_with_the_stage_by_stage_path(name):
     wl = CASES[name]
     inp, out = run(wl)
-    L = _lib.lib()
-    L.mta_set_variant(b"fused", 4)
+    _lib.set_variant("fused", 2)                    # scores + conv, softmax and P V as three launches over score planes
+    _lib.reset_launch_count()
     try:
         _, staged = run(wl, inp)
     finally:
-        L.mta_set_variant(b"fused", 0)
+        _lib.set_variant("fused", 0)
+    assert _lib.launch_count() >= 3
     torch.cuda.synchronize()
     # the two differ only by where the softmax rounds (normalised probabilities against exponentials)
     assert rel_fro(npf(out), npf(staged)) <= 8e-3
@@ -90,3 +91,22 @@ def test_conv_attention_at_b1_h16_s4096(dtype):
     for r0 in starts:
         ref = orc.conv_attn_fwd_rows(*args, 0, r0, r0 + 12, True, None, orc.ROUND_NONE)
         assert_parity(npf(out[0, :, r0:r0 + 12]), ref, dtype, f"rows [{r0},{r0 + 12})")
+
+
+def test_a_timed_out_wait_is_reported_by_the_next_call_and_cleared_by_device_status():
+    """The host marks the device as a kernel's timed-out wait would (nothing is made to wait on the GPU): the next
+    forward must return status 4 instead of a result, mta_device_status must report and clear the condition, and the
+    forward after that must be right again."""
+    wl = CASES["s257_3x3"]
+    inp, good = run(wl)
+    _lib.device_status()
+    L = _lib.lib()
+    assert L.mta_inject_wait_timeout(torch.cuda.current_stream().cuda_stream) == 0
+    with pytest.raises(_lib.MTALibraryError, match="gave up"):
+        run(wl, inp)
+    with pytest.raises(_lib.MTALibraryError):
+        ops.mta_fused_fwd(*[inp[k].to(DEV) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")], True)
+    assert L.mta_device_status(torch.cuda.current_stream().cuda_stream) == 4
+    assert L.mta_device_status(torch.cuda.current_stream().cuda_stream) == 0
+    _, again = run(wl, inp)
+    assert torch.equal(again, good)

@@ -33,6 +33,7 @@ def run_static(d, wl, causal=True):
 def test_static_scratch_matches_workspace_entry_point_twice():
     L = _lib.lib()
     assert L.mta_static_scratch_bytes() == 64 << 20
+    assert L.mta_static_scratch_prepare() == 0           # start-up: the array's address on this device is looked up here
     cases = [MTAWorkload("na1", 1, 8, 1024, 32, 3, 5, dtype=torch.float32, seed=71),        # exactly the 64 MiB the array holds
              MTAWorkload("na2", 2, 4, 200, 64, 3, 19, dtype=torch.float16, seed=72),        # 19 taps wide: stage by stage, over stale contents
              MTAWorkload("na3", 1, 2, 130, 32, 3, 3, dtype=torch.float32, seed=73),         # CUDA-core path, ragged size
