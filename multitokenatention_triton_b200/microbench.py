@@ -151,7 +151,7 @@ def main():
             _line("pv causal", ms, flops=2.0 * D * N * C * tri, shape=shape + f" D{D}", variant=a.variant,
                   read_gbs=es * N * C * tri / ms / 1e6)
     if a.which in ("conv_attn", "all"):
-        # the fused conv attention softmax(scale * conv(Q K^T)) V (TritonConvAttention): three launches
+        # the conv attention softmax(scale * conv(Q K^T)) V (TritonConvAttention): one kernel for 16-bit causal problems
         g = torch.Generator().manual_seed(5)
         q, k, v = (torch.randn(N, C, S, D, generator=g).to(dtype).to(dev) for _ in range(3))
         w = (torch.randn(C, 6, 11, generator=g) / 66 ** 0.5).to(dtype).to(dev)
