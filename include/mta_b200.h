@@ -165,6 +165,20 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
                   int w_dtype, void* stream);
 
 /*
+ * mta_fused_fwd with dropout on the attention weights between the second head mix and the product with V, where
+ * MTAAttentionTriton.forward applies F.dropout(scores, p=self.dropout, training=self.training)
+ * (mta_attention_triton.py:87).  No mask tensor exists: whether weight (batch, head, query, key) is kept is a function
+ * of (dropout_seed, batch * H + head, query, key) - one Philox4x32-10 block per 8 consecutive keys, counter
+ * (key / 8, query, plane, 0), key = the seed, a key kept when its 16-bit field is below round((1 - p) * 65536) - so
+ * the result does not depend on tiling or on the row range and can be reproduced on the host.  Kept weights are scaled
+ * by 1 / (1 - p) and rounded to the dtype.  0 <= dropout_p < 1; dropout_p = 0 is mta_fused_fwd.
+ */
+int mta_fused_fwd_dropout(const void* q, const void* k, const void* v, const void* w1, const void* W1, const void* w2,
+                          const void* W2, void* o, void* workspace, size_t workspace_bytes, int B, int H, int S, int D,
+                          int cq, int ck, int cq2, int ck2, int q_row_begin, int q_row_end, int causal, int dtype,
+                          int w_dtype, float dropout_p, unsigned long long dropout_seed, void* stream);
+
+/*
  * mta_fused_fwd (all query rows) for a caller whose q, k, v and o live in HOST memory (page-locked memory lets the
  * copies overlap; pageable memory works but serialises them): the batch is cut into chunks of `chunk_batch` batch
  * elements (0 = choose) and three internal CUDA streams overlap the host->device copy of chunk c+1, the forward

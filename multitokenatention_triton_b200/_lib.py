@@ -47,6 +47,7 @@ SIGNATURES = {
     "mta_conv_attn_fwd_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mta_workspace_bytes": (_sz, [_i] * 11),
     "mta_fused_fwd": (_i, [_vp] * 9 + [_sz] + [_i] * 13 + [_vp]),
+    "mta_fused_fwd_dropout": (_i, [_vp] * 9 + [_sz] + [_i] * 13 + [_f, ctypes.c_ulonglong, _vp]),
     "mta_fused_fwd_host": (_i, [_vp] * 8 + [_i] * 12),
     "mta_host_pipeline_release": (_i, []),
     "mta_set_stage_trace": (_i, [_i]),

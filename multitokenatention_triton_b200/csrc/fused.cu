@@ -91,7 +91,19 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
                   const void* W2, void* o, void* workspace, size_t workspace_bytes, int B, int H, int S, int D, int cq,
                   int ck, int cq2, int ck2, int q_row_begin, int q_row_end, int causal, int dtype, int w_dtype,
                   void* stream) {
+    return mta_fused_fwd_dropout(q, k, v, w1, W1, w2, W2, o, workspace, workspace_bytes, B, H, S, D, cq, ck, cq2, ck2, q_row_begin,
+                                 q_row_end, causal, dtype, w_dtype, 0.0f, 0ull, stream);
+}
+
+int mta_fused_fwd_dropout(const void* q, const void* k, const void* v, const void* w1, const void* W1, const void* w2,
+                          const void* W2, void* o, void* workspace, size_t workspace_bytes, int B, int H, int S, int D, int cq,
+                          int ck, int cq2, int ck2, int q_row_begin, int q_row_end, int causal, int dtype, int w_dtype,
+                          float dropout_p, unsigned long long dropout_seed, void* stream) {
     set_error("%s", "");
+    MTA_REQUIRE(dropout_p >= 0.0f && dropout_p < 1.0f, "fused_fwd: dropout probability %g outside [0, 1)", (double)dropout_p);
+    DropoutSpec drop;
+    drop.p = dropout_p;
+    drop.seed = dropout_seed;
     MTA_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "fused_fwd: unknown dtype code (%d, %d)", dtype, w_dtype);
     MTA_REQUIRE(B >= 0 && H >= 1 && S >= 0 && D >= 1, "fused_fwd: bad shape B=%d H=%d S=%d D=%d", B, H, S, D);
     MTA_REQUIRE(cq >= 1 && ck >= 1 && cq2 >= 1 && ck2 >= 1, "fused_fwd: kernel sizes must be positive");
@@ -146,7 +158,7 @@ int mta_fused_fwd(const void* q, const void* k, const void* v, const void* w1, c
     if ((rc = trace_mark("head_mix2", st))) return rc;
     if ((rc = head_linear_launch(bufB, pv, W2, w_dtype, bufA, pv, B, H, S, S, causal, 0.0f, pl.r0, pl.r1, false, dtype, st))) return rc;
     if ((rc = trace_mark("pv", st))) return rc;
-    if ((rc = pv_launch(bufA, pv, pl.r1 - pl.ra, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st))) return rc;
+    if ((rc = pv_launch(bufA, pv, pl.r1 - pl.ra, v, o, B, H, S, D, causal, pl.r0, pl.r1, dtype, st, drop))) return rc;
     return trace_end(st);
 }
 

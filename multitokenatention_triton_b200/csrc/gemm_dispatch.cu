@@ -17,14 +17,14 @@ int qk_scores_launch(const void* q, const void* k, void* s, PlaneView sv, int B,
 }
 
 int pv_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
-              int causal, int row_begin, int row_end, int dtype, cudaStream_t st) {
+              int causal, int row_begin, int row_end, int dtype, cudaStream_t st, DropoutSpec drop) {
     if (B == 0 || row_end <= row_begin) return MTA_OK;
     const int want = variant("gemm");
     const bool ok = tc05_contractions_supported(S, D, dtype, p, v, o, pview);
     MTA_REQUIRE(want != 2 || ok, "pv: the tensor-core variant needs a 16-bit dtype, D in {64,128}, S %% 8 == 0 and 16-byte aligned tensors");
     if (ok && want != 1)
-        return pv_tc05_launch(p, pview, p_rows_stored, v, o, B, H, S, D, causal, row_begin, row_end, dtype, st);
-    return pv_simt_launch(p, pview, v, o, B, H, S, D, causal, row_begin, row_end, dtype, st);
+        return pv_tc05_launch(p, pview, p_rows_stored, v, o, B, H, S, D, causal, row_begin, row_end, dtype, st, drop);
+    return pv_simt_launch(p, pview, v, o, B, H, S, D, causal, row_begin, row_end, dtype, st, drop);
 }
 
 }  // namespace mta

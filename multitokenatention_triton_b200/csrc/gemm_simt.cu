@@ -66,7 +66,7 @@ qk_scores_simt_kernel(const T* __restrict__ q, const T* __restrict__ k, T* __res
 template <typename T>
 __global__ void __launch_bounds__(GT)
 pv_simt_kernel(const T* __restrict__ p, PlaneView pv, const T* __restrict__ v, T* __restrict__ o, int S, int D,
-               int causal, int row_begin, int row_end, int tiles_d) {
+               int causal, int row_begin, int row_end, int tiles_d, DropoutSpec drop) {
     __shared__ float ps[BK][BT + 1];
     __shared__ float vs[BK][BT + 1];
     const long bh = blockIdx.y;
@@ -84,6 +84,10 @@ pv_simt_kernel(const T* __restrict__ p, PlaneView pv, const T* __restrict__ v, T
                 const int qq = q0 + r;
                 float val = 0.0f;
                 if (qq < q_end && kk < k_end && (!causal || kk <= qq)) val = to_f32<T>(p[pv.at(bh, qq, kk)]);
+                if (drop.on() && val != 0.0f) {
+                    const uint32_t keep = dropout_keep8(drop.seed, (uint32_t)bh, (uint32_t)qq, (uint32_t)(kk >> 3), drop.keep_threshold());
+                    val = (keep >> (kk & 7)) & 1u ? round_to<T>(val * drop.scale()) : 0.0f;
+                }
                 ps[idx % BK][r] = val;
             }
             {   // V: BK keys x BT features, consecutive threads along features
@@ -137,12 +141,12 @@ int qk_scores_simt_launch(const void* q, const void* k, void* s, PlaneView sv, i
 }
 
 int pv_simt_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
-                   int row_begin, int row_end, int dtype, cudaStream_t st) {
+                   int row_begin, int row_end, int dtype, cudaStream_t st, DropoutSpec drop) {
     const int tiles_q = (row_end - row_begin + BT - 1) / BT, tiles_d = (D + BT - 1) / BT;
     dim3 grid((unsigned)(tiles_q * tiles_d), (unsigned)(B * H));
 #define MTA_PV(TT)                                                                                              \
     pv_simt_kernel<TT><<<grid, GT, 0, st>>>(static_cast<const TT*>(p), pview, static_cast<const TT*>(v),          \
-                                            static_cast<TT*>(o), S, D, causal, row_begin, row_end, tiles_d)
+                                            static_cast<TT*>(o), S, D, causal, row_begin, row_end, tiles_d, drop)
     if (dtype == MTA_F32) MTA_PV(float);
     else if (dtype == MTA_BF16) MTA_PV(__nv_bfloat16);
     else MTA_PV(__half);

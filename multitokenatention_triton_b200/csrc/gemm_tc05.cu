@@ -185,17 +185,19 @@ constexpr int PV_KEYS = 64;               // keys per pipeline stage: 32 KB stag
                                           // start-up and epilogue overlap the other's steady state
 constexpr int PV_VBOX_BYTES = PV_KEYS * 128;   // one box of the V tile: 64 keys x 64 elements
 
-template <typename T, int D>
+// DROP: the four epilogue warps, idle until the accumulator is complete, apply the dropout of dropout.cuh to every P tile
+// in shared memory before its MMAs are issued (a thread owns a row of the tile).
+template <typename T, int D, bool DROP>
 __global__ void __launch_bounds__(PV_THREADS)
 pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ CUtensorMap mv, T* __restrict__ o,
-               int p_row0, int S, int causal, int row_begin, int row_end, int* err_flag) {
+               int p_row0, int S, int causal, int row_begin, int row_end, int* err_flag, DropoutSpec drop) {
     constexpr int NBOX_V = D / 64;
     constexpr int P_BYTES = BOX_BYTES;                     // 128 q x 64 k
     constexpr int V_BYTES = NBOX_V * PV_VBOX_BYTES;        // 64 k x D
     constexpr int STAGE_BYTES = P_BYTES + V_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align_1024(smem_raw);
-    __shared__ __align__(8) uint64_t full_bar[PV_STAGES], empty_bar[PV_STAGES], acc_bar;
+    __shared__ __align__(8) uint64_t full_bar[PV_STAGES], empty_bar[PV_STAGES], mask_bar[PV_STAGES], acc_bar;
     __shared__ uint32_t tmem_slot;
 
     __shared__ int abort_flag;      // an earlier bounded wait on this device gave up: the whole CTA does nothing
@@ -217,6 +219,7 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
             for (int i = 0; i < PV_STAGES; ++i) {
                 mbar_init(&full_bar[i], 1);
                 mbar_init(&empty_bar[i], 1);
+                mbar_init(&mask_bar[i], 4);
             }
             mbar_init(&acc_bar, 1);
             fence_mbar_init();
@@ -251,6 +254,7 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
             uint8_t* sp = smem + st * STAGE_BYTES;
             uint8_t* sv = sp + P_BYTES;
             mbar_wait(&full_bar[st], use & 1, err_flag);
+            if (DROP) mbar_wait(&mask_bar[st], use & 1, err_flag);         // the epilogue warps have applied the dropout
             const int k0 = kt * PV_KEYS;
             if (causal && k0 + PV_KEYS - 1 > q0) {
                 // Keys above the diagonal must contribute nothing, whatever the buffer holds there.
@@ -285,6 +289,26 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
             __syncwarp();
         }
     } else {
+        if (DROP) {
+            const int r = (int)threadIdx.x - 64;             // row of the P tile this thread owns
+            const uint32_t thr = drop.keep_threshold();
+            const float scale = drop.scale();
+            for (int kt = 0; kt < nk; ++kt) {
+                const int st = kt % PV_STAGES, use = kt / PV_STAGES;
+                uint8_t* sp = smem + st * STAGE_BYTES;
+                mbar_wait(&full_bar[st], use & 1, err_flag);
+#pragma unroll 2
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint32_t keep = dropout_keep8(drop.seed, (uint32_t)bh, (uint32_t)(q0 + r), (uint32_t)(kt * (PV_KEYS / 8) + ch), thr);
+                    T* e8 = reinterpret_cast<T*>(sp + r * 128 + ((ch ^ (r & 7)) << 4));
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) e8[e] = (keep >> e) & 1u ? from_f32<T>(to_f32<T>(e8[e]) * scale) : from_f32<T>(0.0f);
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&mask_bar[st]);
+            }
+        }
         mbar_wait(&acc_bar, 0, err_flag);
         __syncwarp();
         fence_after_sync();
@@ -315,7 +339,7 @@ pv_tc05_kernel(const __grid_constant__ CUtensorMap mp, const __grid_constant__ C
 
 template <typename T, int D>
 int launch_pv(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int causal, int row_begin,
-              int row_end, long p_rows_stored, cudaStream_t st) {
+              int row_end, long p_rows_stored, cudaStream_t st, DropoutSpec drop) {
     CUtensorMap mp, mv;
     int rc;
     if ((rc = make_tensor_map_3d(&mp, p, (uint64_t)B * H, (uint64_t)p_rows_stored, S, S, (uint64_t)pview.plane_stride, 64, TILE, true))) return rc;
@@ -324,10 +348,16 @@ int launch_pv(const void* p, PlaneView pview, const void* v, void* o, int B, int
     if ((rc = wait_flag_ptr(&flag))) return rc;
     const int n_qt = (row_end - row_begin + TILE - 1) / TILE;
     const size_t smem = (size_t)PV_STAGES * (BOX_BYTES + (D / 64) * PV_VBOX_BYTES) + 1024;
-    MTA_CUDA_OK(cudaFuncSetAttribute(pv_tc05_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)n_qt, (unsigned)(B * H));
-    pv_tc05_kernel<T, D><<<grid, PV_THREADS, smem, st>>>(mp, mv, static_cast<T*>(o), pview.row0, S, causal, row_begin,
-                                                         row_end, flag);
+    if (drop.on()) {
+        MTA_CUDA_OK(cudaFuncSetAttribute(pv_tc05_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        pv_tc05_kernel<T, D, true><<<grid, PV_THREADS, smem, st>>>(mp, mv, static_cast<T*>(o), pview.row0, S, causal, row_begin,
+                                                                   row_end, flag, drop);
+    } else {
+        MTA_CUDA_OK(cudaFuncSetAttribute(pv_tc05_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        pv_tc05_kernel<T, D, false><<<grid, PV_THREADS, smem, st>>>(mp, mv, static_cast<T*>(o), pview.row0, S, causal, row_begin,
+                                                                    row_end, flag, drop);
+    }
     MTA_LAUNCH_OK("pv_tc05_kernel");
     return MTA_OK;
 }
@@ -340,8 +370,8 @@ bool tc05_contractions_supported(int S, int D, int dtype, const void* a, const v
 }
 
 int pv_tc05_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
-                   int causal, int row_begin, int row_end, int dtype, cudaStream_t st) {
-#define MTA_PV(TT, DD) return launch_pv<TT, DD>(p, pview, v, o, B, H, S, causal, row_begin, row_end, p_rows_stored, st)
+                   int causal, int row_begin, int row_end, int dtype, cudaStream_t st, DropoutSpec drop) {
+#define MTA_PV(TT, DD) return launch_pv<TT, DD>(p, pview, v, o, B, H, S, causal, row_begin, row_end, p_rows_stored, st, drop)
     if (dtype == MTA_BF16) { if (D == 64) MTA_PV(__nv_bfloat16, 64); MTA_PV(__nv_bfloat16, 128); }
     if (D == 64) MTA_PV(__half, 64);
     MTA_PV(__half, 128);

@@ -3,6 +3,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "dropout.cuh"
 
 namespace mta {
 
@@ -51,14 +52,15 @@ int qk_scores_launch(const void* q, const void* k, void* s, PlaneView sv, int B,
                      int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 
 // o[rows] = p[rows, k<=q] V.  `p_rows_stored` = number of rows each plane of p holds (from pview.row0 on).
+// `drop`: dropout on the weights as they are read (dropout.cuh); the default leaves them as they are.
 int pv_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
-              int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
+              int causal, int row_begin, int row_end, int dtype, cudaStream_t st, DropoutSpec drop = DropoutSpec());
 
 // CUDA-core versions of the two contractions (gemm_simt.cu).
 int qk_scores_simt_launch(const void* q, const void* k, void* s, PlaneView sv, int B, int H, int S, int D, float scale,
                           int round_scale, int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
 int pv_simt_launch(const void* p, PlaneView pview, const void* v, void* o, int B, int H, int S, int D, int causal,
-                   int row_begin, int row_end, int dtype, cudaStream_t st);
+                   int row_begin, int row_end, int dtype, cudaStream_t st, DropoutSpec drop = DropoutSpec());
 
 // tcgen05 version of the conv (conv2d_tc05.cu): 16-bit dtypes, S <= 17, W a multiple of 8, R small enough for its
 // shared-memory rings (R <= 13 with 16-bit weights).
@@ -73,7 +75,7 @@ int conv2d_tc05_launch(const void* x, PlaneView xv, long x_rows_stored, const vo
 // tcgen05 tensor-core versions (gemm_tc05.cu): 16-bit dtypes, D in {64,128}, S a multiple of 8.
 bool tc05_contractions_supported(int S, int D, int dtype, const void* a, const void* b, const void* c, PlaneView view);
 int pv_tc05_launch(const void* p, PlaneView pview, long p_rows_stored, const void* v, void* o, int B, int H, int S, int D,
-                   int causal, int row_begin, int row_end, int dtype, cudaStream_t st);
+                   int causal, int row_begin, int row_end, int dtype, cudaStream_t st, DropoutSpec drop = DropoutSpec());
 // Persistent, warp-specialised score-tile kernel (qk_persistent.cu); same domain as the kernels above.
 // NI = 1: c = scale * a b^T.  mode 0: all tiles with keys <= query; 1 / 2: the band of a (band_cq x (2 band_pw + 1))
 // conv / the tiles wholly below it.

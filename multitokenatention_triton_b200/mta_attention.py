@@ -61,10 +61,13 @@ class MTAAttentionTriton(nn.Module):
         if not self.causal:
             raise NotImplementedError("MTAAttentionTriton without a mask requires causal=True, as in the reference's benchmarks")
         dropping = self.training and self.dropout > 0.0
-        if self.fused and not dropping and not (torch.is_grad_enabled() and any(
-                t.requires_grad for t in (xq, xk, xv, *self.parameters()))):
+        if self.fused and not (torch.is_grad_enabled() and any(t.requires_grad for t in (xq, xk, xv, *self.parameters()))):
+            # F.dropout(scores, p=self.dropout, training=self.training) (mta_attention_triton.py:87) runs inside the last
+            # kernel; its seed is drawn from torch's CPU generator, so torch.manual_seed makes a forward repeatable
+            seed = int(torch.randint(0, 2 ** 62, (1,), dtype=torch.int64).item()) if dropping else 0
             out = ops.mta_fused_fwd(xq, xk, xv, self.mta_conv_triton.effective_weight(), self.wpsm_triton.weight,
-                                    self.mta_conv_after_sm_triton.effective_weight(), self.wposm_triton.weight, causal=True)
+                                    self.mta_conv_after_sm_triton.effective_weight(), self.wposm_triton.weight, causal=True,
+                                    dropout_p=self.dropout if dropping else 0.0, dropout_seed=seed)
             return out.transpose(1, 2)
         # stage by stage; every stage is differentiable (the conv and the head mix through their backward kernels, the
         # scores, the softmax and the product with V through autograd_ops), so this is the path a training step uses

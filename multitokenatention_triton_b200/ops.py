@@ -202,9 +202,10 @@ def conv_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, weight: tor
 def mta_fused_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w1: torch.Tensor, W1: torch.Tensor,
                   w2: torch.Tensor, W2: torch.Tensor, causal: bool = True,
                   rows: Optional[Tuple[int, int]] = None, out: Optional[torch.Tensor] = None,
-                  workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  workspace: Optional[torch.Tensor] = None, dropout_p: float = 0.0, dropout_seed: int = 0) -> torch.Tensor:
     """Full four-stage MTA forward; returns (B,H,S,D) contiguous.  With `rows=(r0,r1)` only those query rows
-    of the output are written (the rest of a fresh output is zero)."""
+    of the output are written (the rest of a fresh output is zero).  `dropout_p` > 0 drops attention weights before
+    the product with V inside the kernel (keep decisions are a function of `dropout_seed` and the weight's position)."""
     q, k, v = _cuda_contig(q, "xq"), _cuda_contig(k, "xk"), _cuda_contig(v, "xv")
     B, H, S, D = q.shape
     assert k.shape == q.shape and v.shape == q.shape
@@ -223,9 +224,10 @@ def mta_fused_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w1: torch.T
     if workspace is None or workspace.numel() < nbytes:
         workspace = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
-        check(L.mta_fused_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), w1.data_ptr(), W1.data_ptr(), w2.data_ptr(),
-                              W2.data_ptr(), out.data_ptr(), workspace.data_ptr(), workspace.numel(), B, H, S, D, cq, ck,
-                              cq2, ck2, r0, r1, int(bool(causal)), dtype_code(q), dtype_code(w1), stream_ptr(q.device)),
+        check(L.mta_fused_fwd_dropout(q.data_ptr(), k.data_ptr(), v.data_ptr(), w1.data_ptr(), W1.data_ptr(), w2.data_ptr(),
+                                      W2.data_ptr(), out.data_ptr(), workspace.data_ptr(), workspace.numel(), B, H, S, D, cq, ck,
+                                      cq2, ck2, r0, r1, int(bool(causal)), dtype_code(q), dtype_code(w1), float(dropout_p),
+                                      int(dropout_seed) & 0xFFFFFFFFFFFFFFFF, stream_ptr(q.device)),
               "mta_fused_fwd")
     return out
 

@@ -241,3 +241,54 @@ def mta_fwd_masked(q, k, v, w1, W1, w2, W2, mask, causal: bool = True, pad_key: 
     probs = np.where(dead, 0.0, probs).astype(np.float32)
     probs = head_linear(probs, W2, causal, 0.0)
     return np.einsum("bhqk,bhkd->bhqd", probs.astype(np.float64), v.astype(np.float64)).astype(np.float32)
+
+
+# ---- dropout of the attention weights (host restatement of the library's position-keyed mask) -------------------------
+def philox4x32_10(c0, c1, c2, c3, k0, k1):
+    """Philox4x32 with 10 rounds (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC11) on
+    numpy uint32 arrays; returns the four output words."""
+    M0, M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+    W0, W1 = 0x9E3779B9, 0xBB67AE85
+    c0, c1, c2, c3 = (np.asarray(c, dtype=np.uint32) for c in (c0, c1, c2, c3))
+    c0, c1, c2, c3 = np.broadcast_arrays(c0, c1, c2, c3)
+    k0, k1 = int(k0) & 0xFFFFFFFF, int(k1) & 0xFFFFFFFF
+    mask32 = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = M0 * c0.astype(np.uint64)
+        p1 = M1 * c2.astype(np.uint64)
+        hi0, lo0 = (p0 >> np.uint64(32)).astype(np.uint32), (p0 & mask32).astype(np.uint32)
+        hi1, lo1 = (p1 >> np.uint64(32)).astype(np.uint32), (p1 & mask32).astype(np.uint32)
+        c0, c1, c2, c3 = hi1 ^ c1 ^ np.uint32(k0), lo1, hi0 ^ c3 ^ np.uint32(k1), lo0
+        k0, k1 = (k0 + W0) & 0xFFFFFFFF, (k1 + W1) & 0xFFFFFFFF
+    return c0, c1, c2, c3
+
+
+def dropout_keep_mask(seed: int, planes: int, S: int, p: float) -> np.ndarray:
+    """(planes, S, S) boolean: weight (plane, query, key) is kept.  One Philox block per 8 consecutive keys, counter
+    (key // 8, query, plane, 0), key = the 64-bit seed; key 8c + e takes the e-th 16-bit field of the 128 output bits and is
+    kept when the field is below round((1 - p) * 65536) - the function the library's P.V kernels evaluate."""
+    thr = int(min(65536.0, max(0.0, np.float32(np.float32(1.0 - np.float32(p)) * np.float32(65536.0)) + np.float32(0.5))))
+    chunks = (S + 7) // 8
+    c0 = np.arange(chunks, dtype=np.uint32)[None, None, :]
+    c1 = np.arange(S, dtype=np.uint32)[None, :, None]
+    c2 = np.arange(planes, dtype=np.uint32)[:, None, None]
+    out = philox4x32_10(c0, c1, c2, np.uint32(0), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    fields = np.stack([(out[e >> 1] >> np.uint32(16 * (e & 1))) & np.uint32(0xFFFF) for e in range(8)], axis=-1)   # (planes,S,chunks,8)
+    keep = (fields < thr).reshape(planes, S, chunks * 8)[:, :, :S]
+    return keep
+
+
+def mta_fwd_dropout(q, k, v, w1, W1, w2, W2, p: float, seed: int) -> np.ndarray:
+    """The causal forward with the reference's dropout on the attention weights (mta_attention_triton.py:87) under the
+    mask of dropout_keep_mask; composed from the C primitives, small sizes only.  Returns (B,H,S,D) float32."""
+    q, k, v, w1, W1, w2, W2 = map(_f32, (q, k, v, w1, W1, w2, W2))
+    B, H, S, D = q.shape
+    scores = np.tril(np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), k.astype(np.float64)) / np.sqrt(D)).astype(np.float32)
+    scores = conv2d(scores, w1, True)
+    scores = head_linear(scores, W1, True, float("-inf"))
+    probs = softmax(scores, causal=True)
+    probs = conv2d(probs, w2, True)
+    probs = head_linear(probs, W2, True, 0.0)
+    keep = dropout_keep_mask(seed, B * H, S, p).reshape(B, H, S, S)
+    probs = np.where(keep, probs * np.float32(1.0 / (1.0 - p)), np.float32(0.0)).astype(np.float32)
+    return np.einsum("bhqk,bhkd->bhqd", probs.astype(np.float64), v.astype(np.float64)).astype(np.float32)
