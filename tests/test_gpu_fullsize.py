@@ -13,11 +13,24 @@ import torch
 from multitokenatention_triton_b200 import _lib, ops
 from multitokenatention_triton_b200.synthetic import WORKLOADS, make_conv_inputs, make_head_linear_inputs, make_mta_inputs
 from oracle import mta_oracle as orc
-from util import assert_parity, max_abs, npf
+from util import BF16_REL, assert_parity, max_abs, npf, rel_fro, rel_max
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 BF16_ULP = 2.0 ** -8
+
+
+def block_parity(got, args, r0, r1, what):
+    """A block of output rows of a bf16 forward.  Against the oracle with the reference's 16-bit rounding points
+    emulated the library must agree closely (it rounds where the reference rounds); against the exact evaluation the
+    norm-wise 2e-2 holds, while the largest element of so small a block may deviate more - the reference's own bf16
+    pipeline does (the rounding-emulating oracle is up to 2.6e-2 of the block's largest value away from the exact one)."""
+    exact = orc.mta_fwd_rows(*args, 0, r0, r1, True, orc.ROUND_NONE)
+    as_ref = orc.mta_fwd_rows(*args, 0, r0, r1, True, orc.ROUND_BF16)
+    f, m = rel_fro(got, as_ref), rel_max(got, as_ref)
+    assert f <= 4e-3 and m <= 2e-2, f"{what} vs the oracle with the reference's rounding points: rel fro {f:.3e}, rel max {m:.3e}"
+    f = rel_fro(got, exact)
+    assert f <= BF16_REL, f"{what} vs the exact oracle: rel fro {f:.3e}"
 
 
 def test_c2_conv_full_size():
@@ -27,7 +40,9 @@ def test_c2_conv_full_size():
     y = ops.conv2d_fwd(x, w, True)
     _lib.device_status()
     assert torch.count_nonzero(torch.triu(y, diagonal=1)) == 0, "output above the diagonal must be exactly 0"
-    for n, c in ((0, 0), (3, 15), (1, 7)):          # whole planes against the oracle
+    rng = np.random.default_rng(2)
+    planes = [(0, 0), (3, 15)] + [(int(rng.integers(4)), int(rng.integers(16))) for _ in range(2)]
+    for n, c in planes:                              # whole planes (two fixed, two drawn) against the oracle
         ref = orc.conv2d(npf(inp["x"][n:n + 1, c:c + 1]), npf(inp["w"][c:c + 1]), True, orc.ROUND_BF16)
         got = npf(y[n:n + 1, c:c + 1])
         assert max_abs(got, ref) <= 2 * BF16_ULP * max(1.0, np.abs(ref).max())
@@ -50,6 +65,13 @@ def test_c3_head_linear_full_size(fill):
     got = npf(y[1:2, :, :512, :512])
     fin = np.isfinite(ref)
     assert np.array_equal(fin, np.isfinite(got)) and np.max(np.abs(got[fin] - ref[fin])) <= 2 * BF16_ULP
+    # seeded random row blocks of random batch elements against a float32 evaluation of the same einsum
+    rng = np.random.default_rng(3)
+    for _ in range(4):
+        n, r0 = int(rng.integers(4)), int(rng.integers(0, 2048 - 16))
+        r32 = torch.einsum("oh,hpq->opq", W.float(), x[n, :, r0:r0 + 16].float())
+        lowb = ~upper[r0:r0 + 16]
+        assert torch.max(torch.abs(y[n, :, r0:r0 + 16].float() - r32)[..., lowb]) <= 2 * BF16_ULP
     # bottom rows against a float32 evaluation of the same einsum
     r32 = torch.einsum("oh,bhpq->bopq", W.float(), x[:, :, 2040:].float())
     low = ~upper[2040:]
@@ -66,12 +88,13 @@ def test_c4_full_forward_sampled_rows():
     out = ops.mta_fused_fwd(d["q"], d["k"], d["v"], *weights, True)
     _lib.device_status()
     assert torch.isfinite(out).all()
-    for b in (0, 7):
+    rng = np.random.default_rng(4)
+    for b in (0, 7, int(rng.integers(1, 7))):
         one = {k: npf(inp[k][b:b + 1]) for k in ("q", "k", "v")}
         wts = [npf(inp[n]) for n in ("w1", "W1", "w2", "W2")]
-        for r0, r1 in ((0, 16), (2040, 2056), (4080, 4096)):
-            ref = orc.mta_fwd_rows(one["q"], one["k"], one["v"], *wts, 0, r0, r1, True, orc.ROUND_NONE)
-            assert_parity(npf(out[b, :, r0:r1]), ref, wl.dtype, f"c4 b={b} rows [{r0},{r1})")
+        blocks = [(0, 16), (4080, 4096)] + [(r, r + 16) for r in (int(x) for x in rng.integers(16, 4064, size=2))]
+        for r0, r1 in blocks:                        # first rows, last rows and two blocks drawn from the interior
+            block_parity(npf(out[b, :, r0:r1]), (one["q"], one["k"], one["v"], *wts), r0, r1, f"c4 b={b} rows [{r0},{r1})")
     part = torch.zeros_like(out[:2])
     ops.mta_fused_fwd(d["q"][:2], d["k"][:2], d["v"][:2], *weights, True, rows=(1024, 1280), out=part)
     assert torch.equal(part[:, :, 1024:1280], out[:2, :, 1024:1280])
@@ -85,5 +108,6 @@ def test_c5_shape_one_batch_element():
     out = ops.mta_fused_fwd(d["q"], d["k"], d["v"], d["w1"], d["W1"], d["w2"], d["W2"], True)
     _lib.device_status()
     args = [npf(inp[n]) for n in ("q", "k", "v", "w1", "W1", "w2", "W2")]
-    ref = orc.mta_fwd_rows(*args, 0, 8180, 8192, True, orc.ROUND_NONE)
-    assert_parity(npf(out[0, :, 8180:8192]), ref, wl.dtype, "c5 last rows")
+    rng = np.random.default_rng(5)
+    for r0 in [0, 8180] + [int(x) for x in rng.integers(12, 8100, size=2)]:      # first rows, last rows, two interior blocks
+        block_parity(npf(out[0, :, r0:r0 + 12]), args, r0, r0 + 12, f"c5 rows [{r0},{r0 + 12})")
