@@ -22,8 +22,8 @@
 // TMEM (512 columns): conv accumulator 0..127, score accumulator 128..271, P (16-bit, two keys per column) 272..335,
 // O 384..384+D-1.  The kernel is bound by shared-memory bandwidth (the conv MMAs re-read the staged tile once per row
 // tap), which is why P and nothing else that can avoid it goes through shared memory.
-// Work units are taken round-robin in the order (plane, heaviest row block first), so the CTAs that run at the same
-// time share a few planes' K and V through L2 and finish within one unit of one another.
+// Work units are dealt heaviest first in rounds of alternating direction, which balances the CTAs' tile counts to a
+// fraction of a percent (a plain round-robin over (plane, row block) left 10 % between them at B8 H16 S4096).
 // 16-bit dtypes, D in {64, 128}, odd key extent <= 17, causal; any S (TMA zero-fills rows past the end).
 #include "toeplitz_tc05.cuh"
 
@@ -46,7 +46,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 struct CaGeom {
-    int C, S, R, KS, row_begin, row_end, tiles_m, tmo, split_w;
+    int C, S, R, KS, row_begin, row_end, tiles_m, tmo, split_w, planes;
     float score_scale, sm_scale;
     long units;
 };
@@ -121,11 +121,15 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     fence_after_sync();
     const uint32_t tmem = tmem_slot;
 
-    // Every role walks the same sequence: units blockIdx.x, blockIdx.x + gridDim.x, ...; unit u is row block
-    // tiles_m - 1 - u % tiles_m of plane u / tiles_m; n counts the tiles this CTA has started.
+    // Every role walks the same sequence of units.  All units, heaviest row blocks first (row block tm of every plane
+    // before row block tm - 1 of any), are dealt to the CTAs in rounds that alternate direction (0 .. G-1, G-1 .. 0, ...):
+    // a round's units cost the same to within one key tile and the alternation cancels the slope, so the CTAs' tile
+    // counts agree to a fraction of a percent; n counts the tiles this CTA has started.
 #define CA_FOR_UNITS                                                                  \
-    for (long u = blockIdx.x; u < g.units; u += gridDim.x) {                          \
-        const int plane = (int)(u / g.tiles_m), tm = g.tiles_m - 1 - (int)(u % g.tiles_m); \
+    for (long rnd = 0;; ++rnd) {                                                      \
+        const long u = rnd * gridDim.x + ((rnd & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x); \
+        if (u >= g.units) break;                                                      \
+        const int plane = (int)(u % g.planes), tm = g.tiles_m - 1 - (int)(u / g.planes); \
         const int m0 = g.row_begin + tm * g.tmo;                                      \
         const int nk = ca_key_tiles(g, tm);                                           \
         (void)plane; (void)m0;
@@ -394,6 +398,7 @@ int launch_ca(const void* q, const void* k, const void* v, const void* w, int w_
     g.tmo = TM - (R - 1);
     g.tiles_m = (row_end - row_begin + g.tmo - 1) / g.tmo;
     g.split_w = w_dtype == MTA_F32 ? 1 : 0;
+    g.planes = (int)planes;
     g.units = planes * g.tiles_m;
     CUtensorMap mq, mk, mv;
     int rc;
