@@ -205,14 +205,17 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         const float sc = round_to<T>(g.score_scale);
         const bool scaled = g.score_scale != 1.0f;           // raw scores (the conv attention) are rounded once
         int n = 0, un = 0;
-        int tb_head[2] = {-1, -1};                           // head whose slices each of the two sets holds
+        // The weights of a unit's head are fetched one unit ahead (successive units of a CTA belong to different planes,
+        // so every unit rebuilds its slices): the global loads are in flight while the previous unit's tiles are drained.
+        float taps[TAPS_PER_THREAD];
+        if ((long)blockIdx.x < g.units) fetch_taps(taps, w, w_dtype, (int)(blockIdx.x % g.planes) % g.C, R, KS, ft);
         CA_FOR_UNITS
-            const int head = plane % g.C;
-            if (tb_head[un & 1] != head) {
-                // this set was last read by the conv MMAs of unit un - 2, whose tiles all precede tile n - 1
+            {
+                // this set of slices was last read by the conv MMAs of unit un - 2, whose tiles all precede tile n - 1
                 if (n >= 2) mbar_wait(&empty_bar[(n - 2) % NSTAGE], ((n - 2) / NSTAGE) & 1, err_flag);
-                build_toeplitz<T>(tb_base + (un & 1) * tb_bytes, wsm, w, w_dtype, head, R, KS, a_off, g.split_w, ft, 128, 5);
-                tb_head[un & 1] = head;
+                build_from_taps<T>(tb_base + (un & 1) * tb_bytes, wsm, taps, R, KS, a_off, g.split_w, ft, 5);
+                const long u_next = (rnd + 1) * gridDim.x + (((rnd + 1) & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+                if (u_next < g.units) fetch_taps(taps, w, w_dtype, (int)(u_next % g.planes) % g.C, R, KS, ft);
             }
             for (int tn = 0; tn < nk; ++tn, ++n) {
                 const int st = n % NSTAGE;

@@ -91,6 +91,39 @@ __device__ __forceinline__ void issue_conv(uint32_t xa_addr, uint32_t tb_addr, u
 // Called by `nthreads` threads (whole warps, ft = 0 .. nthreads - 1) that own hardware barrier `bar_id`; the head's
 // R x KS weights pass through `wsm` (MAX_TAPS floats of shared memory) so that each is fetched from global memory once.
 constexpr int MAX_TAPS = 16 * 17;
+constexpr int TAPS_PER_THREAD = (MAX_TAPS + 127) / 128;     // with the 128 drain threads as callers
+
+// The two halves of build_toeplitz for a caller that knows its next head ahead of time: fetch_taps reads the head's
+// weights into registers (thread ft of 128 holds taps ft, ft + 128, ...), which hides the global-memory latency behind
+// whatever the caller does next; store_taps / build_from_taps turn them into the slices.
+__device__ __forceinline__ void fetch_taps(float (&reg)[TAPS_PER_THREAD], const void* w, int w_dtype, int head, int R, int KS, int ft) {
+#pragma unroll
+    for (int i = 0; i < TAPS_PER_THREAD; ++i) {
+        const int idx = ft + 128 * i;
+        reg[i] = idx < R * KS ? load_weight(w, (long)head * R * KS + idx, w_dtype) : 0.0f;
+    }
+}
+template <typename T>
+__device__ __forceinline__ void build_from_taps(uint8_t* tb, float* wsm, const float (&reg)[TAPS_PER_THREAD], int R, int KS, int a_off,
+                                                int split_w, int ft, int bar_id) {
+#pragma unroll
+    for (int i = 0; i < TAPS_PER_THREAD; ++i)
+        if (ft + 128 * i < R * KS) wsm[ft + 128 * i] = reg[i];
+    named_barrier(bar_id, 128);
+    const int total = R * 512;
+    for (int idx = ft; idx < total; idx += 128) {
+        const int i = idx >> 9, e = idx & 511;
+        const int nn = e >> 4, kk = e & 15;
+        const int j = kk + 16 - nn - a_off;
+        const float wv = (j >= 0 && j < KS) ? wsm[i * KS + j] : 0.0f;
+        const T hi = from_f32<T>(wv);
+        const int off = i * 1024 + (kk >> 3) * 512 + (nn >> 3) * 128 + (nn & 7) * 16 + (kk & 7) * 2;
+        *reinterpret_cast<T*>(tb + off) = hi;
+        if (split_w) *reinterpret_cast<T*>(tb + R * 1024 + off) = from_f32<T>(wv - to_f32<T>(hi));
+    }
+    named_barrier(bar_id, 128);             // nobody refills wsm while another warp still reads it
+}
+
 template <typename T>
 __device__ __forceinline__ void build_toeplitz(uint8_t* tb, float* wsm, const void* w, int w_dtype, int head, int R, int KS,
                                                int a_off, int split_w, int ft, int nthreads, int bar_id) {
