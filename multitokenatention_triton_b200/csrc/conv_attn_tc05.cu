@@ -183,8 +183,8 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
             const uint32_t tb_addr = smem_u32(tb_base + (un & 1) * tb_bytes);
             for (int tn = 0; tn < nk; ++tn, ++n) {
                 const int st = n % NSTAGE;
-                mbar_wait(&ready_bar[st], (n / NSTAGE) & 1, err_flag);
-                mbar_wait(&acc_empty, (n & 1) ^ 1, err_flag);    // the softmax warps have read the previous conv tile
+                mbar_wait_spin(&ready_bar[st], (n / NSTAGE) & 1, err_flag);
+                mbar_wait_spin(&acc_empty, (n & 1) ^ 1, err_flag);    // the softmax warps have read the previous conv tile
                 fence_after_sync();
                 if (lane == 0) {
                     const uint32_t xa_addr = smem_u32(stage_base + st * TB_OFF);
@@ -258,7 +258,7 @@ conv_attn_tc05_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
             for (int tn = 0; tn < nk; ++tn, ++n) {
                 const int k0 = tn * TN + half * 64;          // key of this thread's first column
                 uint32_t xr[64];
-                mbar_wait(&acc_full, n & 1, err_flag);
+                mbar_wait_spin(&acc_full, n & 1, err_flag);
                 __syncwarp();
                 fence_after_sync();
                 tmem_ld_32x32(tlane + C_COL + (uint32_t)(half * 64), *reinterpret_cast<uint32_t(*)[32]>(&xr[0]));
