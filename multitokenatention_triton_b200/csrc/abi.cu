@@ -12,7 +12,7 @@ thread_local char g_error[512] = "";
 thread_local long g_launches = 0;
 // Kernel selection for tests and measurements: process-wide, read on every launch, written by mta_set_variant from any
 // thread (relaxed atomics: a launch sees either the old or the new value of each key, never a torn one).
-std::atomic<int> g_variant_head_linear{0}, g_variant_conv2d{0}, g_variant_gemm{0}, g_variant_fused{0};
+std::atomic<int> g_variant_head_linear{0}, g_variant_conv2d{0}, g_variant_gemm{0}, g_variant_fused{0}, g_variant_mix_softmax{0};
 }  // namespace
 
 void set_error(const char* fmt, ...) {
@@ -29,6 +29,7 @@ int variant(const char* key) {
     if (!strcmp(key, "conv2d")) return g_variant_conv2d.load(std::memory_order_relaxed);
     if (!strcmp(key, "gemm")) return g_variant_gemm.load(std::memory_order_relaxed);
     if (!strcmp(key, "fused")) return g_variant_fused.load(std::memory_order_relaxed);
+    if (!strcmp(key, "mix_softmax")) return g_variant_mix_softmax.load(std::memory_order_relaxed);
     return 0;
 }
 
@@ -70,6 +71,7 @@ int mta_set_variant(const char* key, int value) {
     else if (!strcmp(key, "conv2d")) g_variant_conv2d.store(value, std::memory_order_relaxed);
     else if (!strcmp(key, "gemm")) g_variant_gemm.store(value, std::memory_order_relaxed);
     else if (!strcmp(key, "fused")) g_variant_fused.store(value, std::memory_order_relaxed);
+    else if (!strcmp(key, "mix_softmax")) g_variant_mix_softmax.store(value, std::memory_order_relaxed);
     else return MTA_ERR_INVALID;
     return MTA_OK;
 }
@@ -126,7 +128,7 @@ int mta_head_linear_softmax_fwd(const void* x, const void* Wm, void* y, int N, i
     if (int rc = check_device()) return rc;
     const PlaneView v = full_view(P, Q);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (variant("fused") != 1 && head_mix_softmax_supported(x, v, y, v, C, Q, 1, x_dtype))
+    if (variant("fused") != 1 && head_mix_softmax_supported(x, v, y, v, C, Q, 1, x_dtype, w_dtype))
         return head_mix_softmax_launch(x, v, Wm, w_dtype, y, v, N, C, Q, 0, P, true, x_dtype, st);
     // shapes the one-pass kernel does not take: the two stages, the softmax in place
     if (int rc = head_linear_launch(x, v, Wm, w_dtype, y, v, N, C, P, Q, 1, 0.0f, 0, P, false, x_dtype, st)) return rc;

@@ -144,7 +144,7 @@ int mta_fused_fwd_dropout(const void* q, const void* k, const void* v, const voi
         if ((rc = conv2d_launch(bufA, pv, pl.r1 - pl.ra, w1, w_dtype, bufB, pv, planes, H, S, S, cq, ck, causal, pl.rb, pl.r1, !causal, dtype, st))) return rc;
     }
     // the first head mix and the softmax run as one kernel where it applies (mta_set_variant("fused", 1) keeps them apart)
-    if (variant("fused") != 1 && head_mix_softmax_supported(bufB, pv, bufA, pv, H, S, causal, dtype)) {
+    if (variant("fused") != 1 && head_mix_softmax_supported(bufB, pv, bufA, pv, H, S, causal, dtype, w_dtype)) {
         if ((rc = trace_mark("head_mix1+softmax", st))) return rc;
         if ((rc = head_mix_softmax_launch(bufB, pv, W1, w_dtype, bufA, pv, B, H, S, pl.rb, pl.r1, false, dtype, st))) return rc;
     } else {

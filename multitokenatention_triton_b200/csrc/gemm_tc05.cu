@@ -97,7 +97,7 @@ int make_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t planes, uint
 
 int make_tensor_map_3d_mode(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
                             uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_cols, uint32_t box_rows,
-                            int swizzle_bytes) {
+                            int swizzle_bytes, uint32_t box_planes) {
     const bool swizzle128 = swizzle_bytes == 128;
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
@@ -108,10 +108,10 @@ int make_tensor_map_3d_mode(CUtensorMap* out, const void* base, uint64_t planes,
                 "tensor map: base and pitches must be multiples of 16 bytes");
     cuuint64_t dims[3] = {cols, rows, planes};
     cuuint64_t strides[2] = {row_pitch_elems * 2, plane_pitch_elems * 2};
-    MTA_REQUIRE(box_cols <= 256 && box_rows <= 256 && (box_cols * 2) % 16 == 0 && (!swizzle128 || box_cols == 64) &&
+    MTA_REQUIRE(box_cols <= 256 && box_rows <= 256 && box_planes >= 1 && box_planes <= 256 && (box_cols * 2) % 16 == 0 && (!swizzle128 || box_cols == 64) &&
                     (swizzle_bytes != 32 || box_cols == 16) && (swizzle_bytes == 0 || swizzle_bytes == 32 || swizzle_bytes == 128),
                 "tensor map: box %u x %u with a %d-byte swizzle is not supported", box_cols, box_rows, swizzle_bytes);
-    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t box[3] = {box_cols, box_rows, box_planes};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE,

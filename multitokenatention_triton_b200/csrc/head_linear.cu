@@ -760,14 +760,29 @@ bool vector_ok(const void* p, PlaneView v) {
 
 }  // namespace
 
-bool head_mix_softmax_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype) {
+namespace {
+bool mix_softmax_mma_ok(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype) {
     return causal && dtype != MTA_F32 && C <= 32 && Q % 8 == 0 && x != y && vector_ok(x, xv) && vector_ok(y, yv);
+}
+}  // namespace
+
+bool head_mix_softmax_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype,
+                                int w_dtype) {
+    return mix_softmax_mma_ok(x, xv, y, yv, C, Q, causal, dtype) ||
+           head_mix_softmax_tc05_supported(x, xv, y, yv, C, Q, causal, dtype, w_dtype);
 }
 
 int head_mix_softmax_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C,
                             int Q, int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st) {
     if (N == 0 || row_end <= row_begin || Q == 0) return MTA_OK;
-    MTA_REQUIRE(head_mix_softmax_supported(x, xv, y, yv, C, Q, 1, dtype),
+    // variant "mix_softmax": 0 auto (tcgen05 where it applies), 1 the mma.sync kernel, 2 tcgen05 or an error
+    const int want = variant("mix_softmax");
+    const bool tc05_able = head_mix_softmax_tc05_supported(x, xv, y, yv, C, Q, 1, dtype, w_dtype);
+    MTA_REQUIRE(want != 2 || tc05_able,
+                "head_mix_softmax: the tcgen05 variant needs 16-bit activations and weights of one dtype and 8, 16, 32, 64 or 128 heads");
+    if (tc05_able && want != 1)
+        return head_mix_softmax_tc05_launch(x, xv, Wm, y, yv, N, C, Q, row_begin, row_end, write_upper, dtype, st);
+    MTA_REQUIRE(mix_softmax_mma_ok(x, xv, y, yv, C, Q, 1, dtype),
                 "head_mix_softmax: needs a 16-bit dtype, C <= 32, Q %% 8 == 0, 16-byte aligned rows and x != y");
     MTA_REQUIRE(N <= 65535, "head_mix_softmax: N = %d exceeds 65535", N);
 #define MTA_MS_CASE(TV, CPV) return launch_mix_softmax<TV, CPV>(x, xv, Wm, w_dtype, y, yv, N, C, Q, row_begin, row_end, write_upper, st)

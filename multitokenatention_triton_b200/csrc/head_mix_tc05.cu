@@ -1,0 +1,433 @@
+// Head mix followed by the causal row softmax on tcgen05 (16-bit dtypes, 16-bit weights, C a power of two in 8..128):
+//   y[n,o,p,:p+1] = softmax_k( round16( sum_h Wm[o,h] * x[n,h,p,k] ) ),   0 above the diagonal up to the end of the key tile
+// (reference: the head mix with fill -inf followed by F.softmax(scores.float(), -1).type_as(xq),
+// mta_attention_triton.py:76-79, triton_linear_head.py:76-139).
+//
+// The mix of R = 128 / C consecutive query rows is ONE matrix product per tile of 128 keys:
+//   D[(r,o)][key] = sum over (h,r') of A[(r,o)][(h,r')] * B[(h,r')][key],
+//   A = the weight repeated on the diagonal blocks (A[(r,o)][(h,r')] = Wm[o,h] when r = r', else 0), built once per CTA,
+//   B = the R rows of all C input planes as they lie in memory (keys contiguous: an MN-major operand), one TMA box of
+//       64 keys x R rows x C planes per half tile.
+// A block-diagonal A wastes R-1 of R multiplications, which the tensor pipe has to spare, and it puts a whole (row, head)
+// on one TMEM lane, keys along the columns: a softmax thread owns one output row of one head and needs no exchange with
+// any other thread for the row statistics.
+//
+// A work unit = (batch element n, group of R rows).  Two passes over the unit's key tiles:
+//   pass 1  tiles 0 .. diagonal: MMA -> TMEM -> round to the 16-bit dtype (the reference's rounding point) -> running
+//           (maximum, sum of exponentials) per thread; nothing is written;
+//   pass 2  the same tiles from the diagonal back to 0 (the input comes from L2: a unit's rows are at most 1 MB):
+//           MMA again -> round -> 2^(x log2 e - shift) -> 16-bit -> global memory, every thread its own row.
+// Recomputing the mix costs tensor time that is free here; in exchange the logits never exist in memory.
+//
+// Warps: 0 TMA producer (ring of HM_NSTAGE tiles of 32 KB), 1-2 MMA issuers on alternate tiles (an issuer also zeroes
+// what lies above the diagonal among the group's R-1 last keys: 0 * NaN must not reach rows for which the key is valid),
+// 4..19 softmax: four groups of four warps, group j owns accumulator j (128 TMEM columns) and takes every fourth tile.
+// Units are dealt heaviest first in rounds of alternating direction, as in conv_attn_tc05.cu.
+#include <algorithm>
+
+#include "kernels.cuh"
+#include "tc05.cuh"
+
+namespace mta {
+namespace {
+using namespace tc05;
+
+constexpr int HM_KEYS = 128;                         // keys per tile = MMA N
+constexpr int HM_BOX_BYTES = 128 * 128;              // one TMA box: 128 (head, row) lines of 64 keys
+constexpr int HM_STAGE_BYTES = 2 * HM_BOX_BYTES;     // a tile: keys 0..63 and 64..127
+constexpr int HM_A_BYTES = 2 * HM_BOX_BYTES;         // the 128 x 128 weight operand: two K blocks of 64
+constexpr int HM_NSTAGE = 4;
+constexpr int HM_NACC = 4;                           // accumulators = softmax groups
+constexpr int HM_SOFTMAX_THREADS = HM_NACC * 128;
+constexpr int HM_ISSUERS = 2;                        // MMA-issuing warps 1..HM_ISSUERS
+// A barrier's consecutive phases must be awaited by ONE thread: a waiter that looks for the phase after next while the
+// next one is still incomplete reads the parity of the phase before as "done" (try_wait tells two phases apart, no more).
+// So the tiles that share a stage, or an accumulator, must all belong to the same issuer.
+static_assert(HM_NSTAGE % HM_ISSUERS == 0 && HM_NACC % HM_ISSUERS == 0, "a stage or accumulator would alternate between issuers");
+constexpr int HM_FIRST_SOFTMAX_WARP = 4;             // a multiple of 4: warp w reads TMEM lanes 32 (w % 4) ..
+constexpr int HM_THREADS = HM_FIRST_SOFTMAX_WARP * 32 + HM_SOFTMAX_THREADS;
+constexpr float HM_LOG2E = 1.4426950408889634f;
+
+template <typename T> struct AbFmtH;
+template <> struct AbFmtH<__nv_bfloat16> { static constexpr int value = 1; };
+template <> struct AbFmtH<__half> { static constexpr int value = 0; };
+
+template <typename T> __device__ __forceinline__ uint32_t hm_pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t hm_pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t hm_pack2<__half>(float lo, float hi) {
+    __half2 r = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+template <typename T> __device__ __forceinline__ void hm_unpack2(uint32_t w, float& lo, float& hi);
+template <> __device__ __forceinline__ void hm_unpack2<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void hm_unpack2<__half>(uint32_t w, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+}
+template <typename T> __device__ __forceinline__ uint32_t hm_max2(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t hm_max2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t hm_max2<__half>(uint32_t a, uint32_t b) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+__device__ __forceinline__ float hm_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// One 32-byte store: a full sector per thread (every thread writes its own row, so nothing coalesces across a warp).
+__device__ __forceinline__ void hm_st_v8(void* p, const uint32_t* w) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+
+struct HmGeom {
+    int N, C, R, Q, row_begin, row_end, groups, write_upper, x_row0;
+    long units;
+};
+
+// Key tiles that the rows of the group starting at p0 reach.
+__device__ __forceinline__ int hm_tiles(const HmGeom& g, int p0) {
+    const int p_last = min(p0 + g.R, g.row_end) - 1;
+    return (min(p_last + 1, g.Q) + HM_KEYS - 1) / HM_KEYS;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(HM_THREADS, 1)
+head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __restrict__ Wm, T* __restrict__ y, PlaneView yv,
+                             HmGeom g, int* err_flag) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t full_bar[HM_NSTAGE], empty_bar[HM_NSTAGE], acc_full[HM_NACC], acc_empty[HM_NACC];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ float stat_m[2][HM_NACC][128], stat_s[2][HM_NACC][128];   // [unit parity][group][lane]
+    uint8_t* a_base = smem;
+    uint8_t* stage_base = smem + HM_A_BYTES;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int C = g.C, R = g.R;
+
+    if (tid == 0) abort_flag = *reinterpret_cast<volatile int*>(err_flag);
+    __syncthreads();
+    if (abort_flag != 0) return;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < HM_NSTAGE; ++i) {
+                mbar_init(&full_bar[i], 1);
+                mbar_init(&empty_bar[i], 1);
+            }
+            for (int i = 0; i < HM_NACC; ++i) {
+                mbar_init(&acc_full[i], 1);
+                mbar_init(&acc_empty[i], 4);
+            }
+            fence_mbar_init();
+            prefetch_tensormap(&mx);
+        }
+        __syncwarp();
+        tmem_alloc(&tmem_slot, 512);
+    }
+    // The weight operand, K-major with the 128-byte swizzle: element (m, k) of K block k / 64 at byte
+    // m * 128 + (((k % 64) / 8) ^ (m % 8)) * 16 + (k % 8) * 2; m = r * C + o, k = h * R + r.
+    for (int i = tid; i < HM_A_BYTES / 16; i += HM_THREADS) reinterpret_cast<uint4*>(a_base)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    for (int i = tid; i < 128 * C; i += HM_THREADS) {
+        const int m = i / C, h = i % C;
+        const int r = m / C, o = m % C;
+        const int k = h * R + r, kk = k & 63;
+        *reinterpret_cast<T*>(a_base + (k >> 6) * HM_BOX_BYTES + m * 128 + (((kk >> 3) ^ (m & 7)) << 4) + (kk & 7) * 2) = Wm[o * C + h];
+    }
+    fence_proxy_async();
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+
+    // Every role walks the same sequence of units and, within a unit, of 2 * nt tiles: pass 1 upwards, pass 2 downwards.
+#define HM_FOR_UNITS                                                                                   \
+    for (long rnd = 0;; ++rnd) {                                                                       \
+        const long u = rnd * gridDim.x + ((rnd & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);        \
+        if (u >= g.units) break;                                                                       \
+        const int n = (int)(u % g.N), p0 = g.row_begin + (g.groups - 1 - (int)(u / g.N)) * R;          \
+        const int nt = hm_tiles(g, p0);                                                                \
+        (void)n;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            HM_FOR_UNITS
+                for (int j = 0; j < 2 * nt && ok; ++j, ++it) {
+                    const int kt = j < nt ? j : 2 * nt - 1 - j;
+                    const int st = it % HM_NSTAGE;
+                    const int use = it / HM_NSTAGE;
+                    if (use > 0 && !(ok = mbar_wait(&empty_bar[st], (uint32_t)((use - 1) & 1), err_flag))) break;
+                    uint8_t* dst = stage_base + st * HM_STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[st], HM_STAGE_BYTES);
+                    tma_load_3d(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C);
+                    tma_load_3d(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C);
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp <= HM_ISSUERS) {
+        // Two issuers take alternate tiles (a thread issues an MMA every ~75 cycles, 8 MMAs a tile would be the kernel's pace).
+        constexpr uint32_t idesc = instr_desc_f16(AbFmtH<T>::value, 0, 1, 128, HM_KEYS);
+        const uint32_t a_addr = smem_u32(a_base);
+        const int issuer = warp - 1;
+        int it = 0;
+        bool ok = true;
+        HM_FOR_UNITS
+            for (int j = 0; j < 2 * nt && ok; ++j, ++it) {
+                if (it % HM_ISSUERS != issuer) continue;
+                const int kt = j < nt ? j : 2 * nt - 1 - j;
+                const int st = it % HM_NSTAGE, ab = it % HM_NACC;
+                const int use = it / HM_NSTAGE, au = it / HM_NACC;
+                uint8_t* sb = stage_base + st * HM_STAGE_BYTES;
+                ok = mbar_wait_spin(&full_bar[st], (uint32_t)(use & 1), err_flag);
+                // Keys above a row's diagonal may hold anything (NaN included) and would reach the later rows of the group
+                // through the zeros of A.  Only keys p0+1 .. p0+R-1 matter (later keys are masked for every row of the
+                // group): in line l = h * R + r', which holds row p0 + r', the keys p0+r'+1 .. p0+R-1 become 0.
+                const int key0 = kt * HM_KEYS;
+                if (p0 + R - 1 >= key0 && p0 + 1 < key0 + HM_KEYS) {
+                    for (int l = lane; l < 128; l += 32) {
+                        uint8_t* line = sb + l * 128;
+                        for (int d = l % R + 1; d < R; ++d) {
+                            const int kk = p0 + d - key0;
+                            if (kk < 0 || kk >= HM_KEYS) continue;
+                            *reinterpret_cast<uint16_t*>(line + (kk >> 6) * HM_BOX_BYTES + ((((kk & 63) >> 3) ^ (l & 7)) << 4) + (kk & 7) * 2) = 0;
+                        }
+                    }
+                    fence_proxy_async();
+                }
+                __syncwarp();
+                if (ok && au > 0) ok = mbar_wait_spin(&acc_empty[ab], (uint32_t)((au - 1) & 1), err_flag);
+                fence_after_sync();
+                if (lane == 0 && ok) {
+                    const uint32_t b_addr = smem_u32(sb);
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint64_t da = smem_desc_sw128(a_addr + (kk >> 2) * HM_BOX_BYTES + (kk & 3) * 32, 16, 1024);
+                        const uint64_t db = smem_desc_sw128(b_addr + kk * 16 * 128, HM_BOX_BYTES, 1024);
+                        mma_f16_ss(tmem + (uint32_t)(ab * HM_KEYS), da, db, idesc, kk > 0 ? 1u : 0u);
+                    }
+                    mma_commit(&empty_bar[st]);
+                    mma_commit(&acc_full[ab]);
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+        }
+    } else if (warp >= HM_FIRST_SOFTMAX_WARP) {
+        const int sw = warp - HM_FIRST_SOFTMAX_WARP, grp = sw >> 2, quarter = warp & 3;   // a warp reads the TMEM lanes of its index modulo 4
+        const int m = quarter * 32 + lane;
+        const int r = m / C, o = m % C;
+        const uint32_t t_base = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(grp * HM_KEYS);
+        // rows start on 32-byte boundaries: the 32-byte stores apply
+        const bool wide = (reinterpret_cast<uintptr_t>(y) & 31u) == 0 && yv.width % 16 == 0 && yv.plane_stride % 16 == 0;
+        int it = 0;
+        int ub = 0;
+        bool ok = true;
+        HM_FOR_UNITS
+            const int p = p0 + r;
+            const bool row_ok = p < g.row_end;
+            const int n_keys = min(p + 1, g.Q);
+            T* yrow = y + yv.at((long)n * C + o, row_ok ? p : p0, 0);
+            // ---- pass 1: statistics over this group's tiles ----
+            float m_run = -INFINITY, s_run = 0.0f;
+            for (int j = 0; j < nt && ok; ++j) {
+                const int t = it + j;
+                if (t % HM_NACC != grp) continue;
+                ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
+                fence_after_sync();
+                const int key0 = j * HM_KEYS;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), v);
+                    tmem_ld_wait();
+                    if (c == 3) {
+                        fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[grp]);
+                    }
+                    const int nvalid = n_keys - (key0 + c * 32);
+                    if (nvalid <= 0) continue;
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) pk[i] = hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) hm_unpack2<T>(pk[i], f[2 * i], f[2 * i + 1]);
+                    float cm;
+                    if (nvalid >= 32) {
+                        uint32_t mx2 = pk[0];
+#pragma unroll
+                        for (int i = 1; i < 16; ++i) mx2 = hm_max2<T>(mx2, pk[i]);
+                        float lo, hi;
+                        hm_unpack2<T>(mx2, lo, hi);
+                        cm = fmaxf(lo, hi);
+                    } else {
+                        cm = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (i >= nvalid) f[i] = -INFINITY;
+                            cm = fmaxf(cm, f[i]);
+                        }
+                    }
+                    if (cm > m_run) {
+                        s_run *= hm_ex2((m_run - cm) * HM_LOG2E);
+                        m_run = cm;
+                    }
+                    const float ml = m_run * HM_LOG2E;
+                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        s0 += hm_ex2(fmaf(f[i], HM_LOG2E, -ml));
+                        s1 += hm_ex2(fmaf(f[i + 1], HM_LOG2E, -ml));
+                        s2 += hm_ex2(fmaf(f[i + 2], HM_LOG2E, -ml));
+                        s3 += hm_ex2(fmaf(f[i + 3], HM_LOG2E, -ml));
+                    }
+                    s_run += (s0 + s1) + (s2 + s3);
+                }
+            }
+            it += nt;
+            // ---- the row's statistics: this thread's and the other three groups' ----
+            stat_m[ub][grp][m] = m_run;
+            stat_s[ub][grp][m] = s_run;
+            named_barrier(1, HM_SOFTMAX_THREADS);
+            float mm = stat_m[ub][0][m], ss = stat_s[ub][0][m];
+#pragma unroll
+            for (int q = 1; q < HM_NACC; ++q) {
+                const float m2 = stat_m[ub][q][m], s2 = stat_s[ub][q][m];
+                const float mn = fmaxf(mm, m2);
+                if (mn != -INFINITY) {
+                    ss = ss * hm_ex2((mm - mn) * HM_LOG2E) + s2 * hm_ex2((m2 - mn) * HM_LOG2E);
+                    mm = mn;
+                }
+            }
+            ub ^= 1;
+            // p = 2^(x log2 e - shift): the division by the sum is folded into the exponent
+            const float shift = fmaf(mm, HM_LOG2E, log2f(ss));
+            // ---- pass 2: the tiles again, from the diagonal down ----
+            for (int j = 0; j < nt && ok; ++j) {
+                const int t = it + j;
+                if (t % HM_NACC != grp) continue;
+                ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
+                fence_after_sync();
+                const int key0 = (nt - 1 - j) * HM_KEYS;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), v);
+                    tmem_ld_wait();
+                    if (c == 3) {
+                        fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[grp]);
+                    }
+                    const int kb = key0 + c * 32;
+                    if (!row_ok || kb >= g.Q) continue;
+                    const int nvalid = n_keys - kb;
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float lo, hi;
+                        hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), lo, hi);
+                        lo = hm_ex2(fmaf(lo, HM_LOG2E, -shift));
+                        hi = hm_ex2(fmaf(hi, HM_LOG2E, -shift));
+                        if (nvalid < 32) {
+                            if (2 * i >= nvalid) lo = 0.0f;
+                            if (2 * i + 1 >= nvalid) hi = 0.0f;
+                        }
+                        pk[i] = hm_pack2<T>(lo, hi);
+                    }
+                    if (wide && kb + 32 <= g.Q) {
+                        hm_st_v8(yrow + kb, pk);
+                        hm_st_v8(yrow + kb + 16, pk + 8);
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(yrow + kb);
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4)
+                            if (kb + q4 * 8 < g.Q) dst[q4] = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    }
+                }
+            }
+            it += nt;
+            if (g.write_upper && grp == 0 && nt * HM_KEYS < g.Q) {
+                // probabilities past the last tile are exactly 0: a warp fills its 32 rows one after the other
+                const long row_off = yv.at((long)n * C + o, row_ok ? p : p0, 0);
+                for (int i = 0; i < 32; ++i) {
+                    const long off = __shfl_sync(0xffffffffu, row_off, i);
+                    if (!__shfl_sync(0xffffffffu, row_ok ? 1 : 0, i)) continue;
+                    for (int k = nt * HM_KEYS + lane * 8; k < g.Q; k += 256) *reinterpret_cast<uint4*>(y + off + k) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            // no early exit after a wait gave up: every softmax warp must meet the others at every unit's barrier
+        }
+    }
+#undef HM_FOR_UNITS
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+constexpr size_t HM_SMEM_BYTES = 1024 + HM_A_BYTES + (size_t)HM_NSTAGE * HM_STAGE_BYTES;
+
+template <typename T>
+int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q, int row_begin, int row_end,
+              bool write_upper, cudaStream_t st) {
+    HmGeom g{};
+    g.N = N; g.C = C; g.R = 128 / C; g.Q = Q; g.row_begin = row_begin; g.row_end = row_end;
+    g.groups = (row_end - row_begin + g.R - 1) / g.R;
+    g.write_upper = write_upper ? 1 : 0;
+    g.x_row0 = xv.row0;
+    g.units = (long)N * g.groups;
+    CUtensorMap mx;
+    int rc;
+    // rows past row_end read as zero: they are lines of the B operand and must not carry anything into the product
+    if ((rc = make_tensor_map_3d_mode(&mx, x, (uint64_t)N * C, (uint64_t)(row_end - xv.row0), (uint64_t)Q, (uint64_t)xv.width,
+                                      (uint64_t)xv.plane_stride, 64, (uint32_t)g.R, 128, (uint32_t)C)))
+        return rc;
+    int* flag = nullptr;
+    if ((rc = wait_flag_ptr(&flag))) return rc;
+    int dev = 0, sms = 0;
+    MTA_CUDA_OK(cudaGetDevice(&dev));
+    MTA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_softmax_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HM_SMEM_BYTES));
+    const unsigned grid = (unsigned)std::min<long>(g.units, sms);
+    head_mix_softmax_tc05_kernel<T><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, static_cast<const T*>(Wm), static_cast<T*>(y), yv, g, flag);
+    MTA_LAUNCH_OK("head_mix_softmax_tc05_kernel");
+    return MTA_OK;
+}
+
+}  // namespace
+
+bool head_mix_softmax_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype,
+                                     int w_dtype) {
+    const bool pow2 = C >= 8 && C <= 128 && (C & (C - 1)) == 0;
+    return causal && dtype != MTA_F32 && w_dtype == dtype && pow2 && Q % 8 == 0 && x != y && aligned16(x) && aligned16(y) &&
+           xv.width % 8 == 0 && xv.plane_stride % 8 == 0 && yv.width % 8 == 0 && yv.plane_stride % 8 == 0;
+}
+
+int head_mix_softmax_tc05_launch(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q,
+                                 int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st) {
+    if (N == 0 || row_end <= row_begin || Q == 0) return MTA_OK;
+    if (dtype == MTA_BF16) return launch_hm<__nv_bfloat16>(x, xv, Wm, y, yv, N, C, Q, row_begin, row_end, write_upper, st);
+    return launch_hm<__half>(x, xv, Wm, y, yv, N, C, Q, row_begin, row_end, write_upper, st);
+}
+
+}  // namespace mta

@@ -39,9 +39,17 @@ int head_linear_bwd_weight_launch(const void* x, const void* dy, float* dW, void
 
 // Head mix followed by the causal row softmax of the mixed logits, in one pass (16-bit dtypes, C <= 32, causal);
 // entries above the diagonal of y are written as 0 when `write_upper`, else left untouched.
-bool head_mix_softmax_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype);
+bool head_mix_softmax_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype,
+                                int w_dtype);
 int head_mix_softmax_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype, void* y, PlaneView yv, int N, int C,
                             int Q, int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st);
+
+// The same on tcgen05 (head_mix_tc05.cu): C a power of two in 8..128, weights in the activations' 16-bit dtype; entries
+// above the diagonal are written as 0 up to the end of the diagonal's 128-key tile, and up to Q when `write_upper`.
+bool head_mix_softmax_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype,
+                                     int w_dtype);
+int head_mix_softmax_tc05_launch(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q,
+                                 int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st);
 
 // Causal row softmax of pre_scale * x; rows [row_begin,row_end).
 int softmax_launch(const void* x, PlaneView xv, void* y, PlaneView yv, long planes, int P, int Q, int causal,

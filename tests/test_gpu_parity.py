@@ -194,6 +194,39 @@ def test_head_linear_softmax(C, S, dtype, variant):
     np.testing.assert_allclose(npf(y).sum(-1), 1.0, atol=4 * ULP[dtype] * np.sqrt(S) + 1e-6)
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("C,S", [(16, 72), (16, 128), (16, 520), (16, 1304), (8, 264), (32, 136), (32, 1032), (64, 200), (128, 136)])
+def test_head_linear_softmax_16bit_weights(C, S, dtype, variant):
+    """Weights in the activations' dtype: the tcgen05 kernel (variant 2: two passes over key tiles, the mix recomputed)
+    and the mma.sync kernel (variant 1, up to 32 heads) against the oracle's two stages; NaN above the diagonal of the
+    input must change nothing."""
+    if variant == 1 and C > 32:
+        pytest.skip("the mma.sync kernel takes up to 32 heads")
+    g = torch.Generator().manual_seed(1900 + C + S)
+    x = (3 * torch.randn(2, C, S, S, generator=g)).to(dtype)
+    W = (torch.eye(C) + 0.5 * torch.randn(C, C, generator=g)).to(dtype)
+    xn = x.clone()
+    iu = torch.triu_indices(S, S, 1)
+    xn[..., iu[0], iu[1]] = float("nan")
+    _lib.set_variant("mix_softmax", variant)
+    try:
+        _lib.reset_launch_count()
+        y = ops.head_linear_softmax_fwd(x.to(DEV), W.to(DEV))
+        assert _lib.launch_count() == 1
+        yn = ops.head_linear_softmax_fwd(xn.to(DEV), W.to(DEV))
+    finally:
+        _lib.set_variant("mix_softmax", 0)
+    _lib.device_status()
+    assert torch.equal(y, yn)
+    mixed = orc.head_linear(npf(x), npf(W), True, float("-inf"), ROUND[dtype])
+    ref = orc.softmax(mixed, True, ROUND[dtype])
+    tol = 2.0 * ULP[dtype] * max(1.0, float(np.max(np.abs(mixed[np.isfinite(mixed)]))))
+    assert max_abs(npf(y), ref) <= tol, f"head mix + softmax C={C} S={S}: {max_abs(npf(y), ref):.3e} > {tol:.3e}"
+    assert np.all(npf(y)[..., iu[0], iu[1]] == 0)
+    np.testing.assert_allclose(npf(y).sum(-1), 1.0, atol=4 * ULP[dtype] * np.sqrt(S) + 1e-6)
+
+
 def test_head_linear_softmax_is_reproducible_and_ignores_upper_input():
     inp = make_head_linear_inputs(1, 16, 264, torch.bfloat16, seed=41)
     x = (inp["x"].float() * 40).to(torch.bfloat16).to(DEV)
