@@ -21,7 +21,7 @@
 //
 // Warps: 0 TMA producer (ring of HM_NSTAGE tiles of 32 KB), 1-2 MMA issuers on alternate tiles (an issuer also zeroes
 // what lies above the diagonal among the group's R-1 last keys: 0 * NaN must not reach rows for which the key is valid),
-// 4..19 softmax: four groups of four warps, group j owns accumulator j (128 TMEM columns) and takes every fourth tile.
+// 3..18 softmax: four groups of four warps, group j owns accumulator j (128 TMEM columns) and takes every fourth tile.
 // Units are dealt heaviest first in rounds of alternating direction, as in conv_attn_tc05.cu.
 #include <algorithm>
 
@@ -39,12 +39,13 @@ constexpr int HM_A_BYTES = 2 * HM_BOX_BYTES;         // the 128 x 128 weight ope
 constexpr int HM_NSTAGE = 4;
 constexpr int HM_NACC = 4;                           // accumulators = softmax groups
 constexpr int HM_SOFTMAX_THREADS = HM_NACC * 128;
+constexpr bool HM_LOAD_HINTS = true, HM_STORE_HINTS = true;   // L2 eviction policies on the TMA loads / the output stores
 constexpr int HM_ISSUERS = 2;                        // MMA-issuing warps 1..HM_ISSUERS
 // A barrier's consecutive phases must be awaited by ONE thread: a waiter that looks for the phase after next while the
 // next one is still incomplete reads the parity of the phase before as "done" (try_wait tells two phases apart, no more).
 // So the tiles that share a stage, or an accumulator, must all belong to the same issuer.
 static_assert(HM_NSTAGE % HM_ISSUERS == 0 && HM_NACC % HM_ISSUERS == 0, "a stage or accumulator would alternate between issuers");
-constexpr int HM_FIRST_SOFTMAX_WARP = 4;             // a multiple of 4: warp w reads TMEM lanes 32 (w % 4) ..
+constexpr int HM_FIRST_SOFTMAX_WARP = 1 + HM_ISSUERS;  // warp w reads TMEM lanes 32 (w % 4) ..: any four consecutive warps cover all lanes
 constexpr int HM_THREADS = HM_FIRST_SOFTMAX_WARP * 32 + HM_SOFTMAX_THREADS;
 constexpr float HM_LOG2E = 1.4426950408889634f;
 
@@ -88,10 +89,87 @@ __device__ __forceinline__ float hm_ex2(float x) {
 }
 
 // One 32-byte store: a full sector per thread (every thread writes its own row, so nothing coalesces across a warp).
-__device__ __forceinline__ void hm_st_v8(void* p, const uint32_t* w) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
-                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+__device__ __forceinline__ void hm_st_v8(void* p, const uint32_t* w, uint64_t policy) {
+    if (HM_STORE_HINTS)
+        asm volatile("st.global.L2::cache_hint.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8}, %9;" ::"l"(p), "r"(w[0]), "r"(w[1]),
+                     "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "l"(policy)
+                     : "memory");
+    else
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                     "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                     : "memory");
+}
+
+// tcgen05.wait::ld that also names the 32 registers of a pending load as in-out operands: nothing that uses them can be
+// scheduled before the wait, and a load into the other buffer may be in flight while this buffer is consumed.
+__device__ __forceinline__ void hm_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                   "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                   "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
                  : "memory");
+}
+
+// Pass 1 on 32 keys of a row: the logits rounded to T, their maximum folded into (m_run, s_run).
+template <typename T>
+__device__ __forceinline__ void hm_stats32(const uint32_t (&v)[32], int nvalid, float& m_run, float& s_run) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pk[i] = hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+    float2 f[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) hm_unpack2<T>(pk[i], f[i].x, f[i].y);
+    float cm;
+    if (nvalid >= 32) {
+        uint32_t mx2 = pk[0];
+#pragma unroll
+        for (int i = 1; i < 16; ++i) mx2 = hm_max2<T>(mx2, pk[i]);
+        float lo, hi;
+        hm_unpack2<T>(mx2, lo, hi);
+        cm = fmaxf(lo, hi);
+    } else {
+        cm = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (2 * i >= nvalid) f[i].x = -INFINITY;
+            if (2 * i + 1 >= nvalid) f[i].y = -INFINITY;
+            cm = fmaxf(cm, fmaxf(f[i].x, f[i].y));
+        }
+    }
+    if (cm > m_run) {
+        s_run *= hm_ex2((m_run - cm) * HM_LOG2E);
+        m_run = cm;
+    }
+    const float2 l2 = make_float2(HM_LOG2E, HM_LOG2E), nm = make_float2(-m_run * HM_LOG2E, -m_run * HM_LOG2E);
+    float2 a0 = make_float2(0.0f, 0.0f), a1 = a0;
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+        const float2 y0 = __ffma2_rn(f[i], l2, nm), y1 = __ffma2_rn(f[i + 1], l2, nm);
+        a0 = __fadd2_rn(a0, make_float2(hm_ex2(y0.x), hm_ex2(y0.y)));
+        a1 = __fadd2_rn(a1, make_float2(hm_ex2(y1.x), hm_ex2(y1.y)));
+    }
+    a0 = __fadd2_rn(a0, a1);
+    s_run += a0.x + a0.y;
+}
+
+// Pass 2 on 32 keys: the logits rounded to T -> probabilities in T, two per word; keys from nvalid on become 0.
+template <typename T>
+__device__ __forceinline__ void hm_prob32(const uint32_t (&v)[32], int nvalid, float shift, uint32_t (&pk)[16]) {
+    const float2 l2 = make_float2(HM_LOG2E, HM_LOG2E), ns = make_float2(-shift, -shift);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float2 f;
+        hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), f.x, f.y);
+        const float2 yv = __ffma2_rn(f, l2, ns);
+        float lo = hm_ex2(yv.x), hi = hm_ex2(yv.y);
+        if (nvalid < 32) {
+            if (2 * i >= nvalid) lo = 0.0f;
+            if (2 * i + 1 >= nvalid) hi = 0.0f;
+        }
+        pk[i] = hm_pack2<T>(lo, hi);
+    }
 }
 
 struct HmGeom {
@@ -157,16 +235,24 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
     const uint32_t tmem = tmem_slot;
 
     // Every role walks the same sequence of units and, within a unit, of 2 * nt tiles: pass 1 upwards, pass 2 downwards.
+    // Units, heaviest first, are dealt to the CTAs in rounds of alternating direction (equal tile counts per CTA, as in
+    // conv_attn_tc05.cu).  Even CTAs take their rounds first to last, odd CTAs last to first: at any moment half of the
+    // CTAs work on long rows and half on short ones, so that the inputs of the units in flight (128 lines x the row
+    // length each, up to 1 MB) add up to about half of L2 and pass 2 finds its tiles there.
+    const long n_rounds = (g.units + gridDim.x - 1) / gridDim.x;
 #define HM_FOR_UNITS                                                                                   \
-    for (long rnd = 0;; ++rnd) {                                                                       \
+    for (long ri = 0; ri < n_rounds; ++ri) {                                                           \
+        const long rnd = (blockIdx.x & 1) ? n_rounds - 1 - ri : ri;                                    \
         const long u = rnd * gridDim.x + ((rnd & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);        \
-        if (u >= g.units) break;                                                                       \
+        if (u >= g.units) continue;                                                                    \
         const int n = (int)(u % g.N), p0 = g.row_begin + (g.groups - 1 - (int)(u / g.N)) * R;          \
         const int nt = hm_tiles(g, p0);                                                                \
         (void)n;
 
     if (warp == 0) {
         if (lane == 0) {
+            // Pass 1 asks L2 to keep what it reads (pass 2 reads it again within the unit), pass 2 reads it for the last time.
+            const uint64_t pol_keep = HM_LOAD_HINTS ? l2_policy_evict_last() : 0, pol_drop = HM_LOAD_HINTS ? l2_policy_evict_first() : 0;
             int it = 0;
             bool ok = true;
             HM_FOR_UNITS
@@ -177,8 +263,14 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
                     if (use > 0 && !(ok = mbar_wait(&empty_bar[st], (uint32_t)((use - 1) & 1), err_flag))) break;
                     uint8_t* dst = stage_base + st * HM_STAGE_BYTES;
                     mbar_expect_tx(&full_bar[st], HM_STAGE_BYTES);
-                    tma_load_3d(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C);
-                    tma_load_3d(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C);
+                    if (HM_LOAD_HINTS) {
+                        const uint64_t pol = j < nt ? pol_keep : pol_drop;
+                        tma_load_3d_hint(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C, pol);
+                        tma_load_3d_hint(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C, pol);
+                    } else {
+                        tma_load_3d(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C);
+                        tma_load_3d(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C);
+                    }
                 }
                 if (!ok) break;
             }
@@ -203,12 +295,20 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
                 // group): in line l = h * R + r', which holds row p0 + r', the keys p0+r'+1 .. p0+R-1 become 0.
                 const int key0 = kt * HM_KEYS;
                 if (p0 + R - 1 >= key0 && p0 + 1 < key0 + HM_KEYS) {
+                    // the 16-byte pieces (8 keys) that hold keys p0+1 .. p0+R-1 of this tile: one when p0 is a multiple of 8
+                    const int c_lo = max(p0 + 1 - key0, 0) >> 3, c_hi = min(p0 + R - 1 - key0, HM_KEYS - 1) >> 3;
                     for (int l = lane; l < 128; l += 32) {
-                        uint8_t* line = sb + l * 128;
-                        for (int d = l % R + 1; d < R; ++d) {
-                            const int kk = p0 + d - key0;
-                            if (kk < 0 || kk >= HM_KEYS) continue;
-                            *reinterpret_cast<uint16_t*>(line + (kk >> 6) * HM_BOX_BYTES + ((((kk & 63) >> 3) ^ (l & 7)) << 4) + (kk & 7) * 2) = 0;
+                        const int lim = p0 + l % R - key0;                  // last key of the tile that row p0 + r' may see
+                        for (int c = c_lo; c <= c_hi; ++c) {
+                            uint4* piece = reinterpret_cast<uint4*>(sb + (c >> 3) * HM_BOX_BYTES + l * 128 + (((c & 7) ^ (l & 7)) << 4));
+                            uint4 w = *piece;
+                            uint32_t* ww = &w.x;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int k = c * 8 + 2 * e;
+                                ww[e] &= (k > lim ? 0u : 0x0000ffffu) | (k + 1 > lim ? 0u : 0xffff0000u);
+                            }
+                            *piece = w;
                         }
                     }
                     fence_proxy_async();
@@ -238,6 +338,7 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
         const uint32_t t_base = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(grp * HM_KEYS);
         // rows start on 32-byte boundaries: the 32-byte stores apply
         const bool wide = (reinterpret_cast<uintptr_t>(y) & 31u) == 0 && yv.width % 16 == 0 && yv.plane_stride % 16 == 0;
+        const uint64_t pol_out = l2_policy_evict_first();   // the output streams through L2: it must not displace the unit's input
         int it = 0;
         int ub = 0;
         bool ok = true;
@@ -254,54 +355,22 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
                 ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = j * HM_KEYS;
-#pragma unroll 1
+                // the load of the next 32 columns is in flight while these are consumed
+                uint32_t va[32], vb[32];
+                tmem_ld_32x32(t_base, va);
+#pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), v);
-                    tmem_ld_wait();
-                    if (c == 3) {
+                    uint32_t (&cur)[32] = (c & 1) ? vb : va;
+                    hm_ld_wait(cur);
+                    if (c < 3) {
+                        tmem_ld_32x32(t_base + (uint32_t)((c + 1) * 32), (c & 1) ? va : vb);
+                    } else {
                         fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[grp]);
                     }
                     const int nvalid = n_keys - (key0 + c * 32);
-                    if (nvalid <= 0) continue;
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) pk[i] = hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                    float f[32];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) hm_unpack2<T>(pk[i], f[2 * i], f[2 * i + 1]);
-                    float cm;
-                    if (nvalid >= 32) {
-                        uint32_t mx2 = pk[0];
-#pragma unroll
-                        for (int i = 1; i < 16; ++i) mx2 = hm_max2<T>(mx2, pk[i]);
-                        float lo, hi;
-                        hm_unpack2<T>(mx2, lo, hi);
-                        cm = fmaxf(lo, hi);
-                    } else {
-                        cm = -INFINITY;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (i >= nvalid) f[i] = -INFINITY;
-                            cm = fmaxf(cm, f[i]);
-                        }
-                    }
-                    if (cm > m_run) {
-                        s_run *= hm_ex2((m_run - cm) * HM_LOG2E);
-                        m_run = cm;
-                    }
-                    const float ml = m_run * HM_LOG2E;
-                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        s0 += hm_ex2(fmaf(f[i], HM_LOG2E, -ml));
-                        s1 += hm_ex2(fmaf(f[i + 1], HM_LOG2E, -ml));
-                        s2 += hm_ex2(fmaf(f[i + 2], HM_LOG2E, -ml));
-                        s3 += hm_ex2(fmaf(f[i + 3], HM_LOG2E, -ml));
-                    }
-                    s_run += (s0 + s1) + (s2 + s3);
+                    if (nvalid > 0) hm_stats32<T>(cur, nvalid, m_run, s_run);
                 }
             }
             it += nt;
@@ -309,10 +378,14 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
             stat_m[ub][grp][m] = m_run;
             stat_s[ub][grp][m] = s_run;
             named_barrier(1, HM_SOFTMAX_THREADS);
-            float mm = stat_m[ub][0][m], ss = stat_s[ub][0][m];
+            // Merged in the order of the tile classes j % 4 = 0, 1, 2, 3 (class c went to group (it0 + c) % 4, it0 = the CTA's
+            // tile count when the unit began): a row's result does not depend on what the CTA did before, so a row range
+            // computed alone is bit-identical to the same rows of a full run.
+            const int it0 = it - nt;
+            float mm = stat_m[ub][it0 % HM_NACC][m], ss = stat_s[ub][it0 % HM_NACC][m];
 #pragma unroll
             for (int q = 1; q < HM_NACC; ++q) {
-                const float m2 = stat_m[ub][q][m], s2 = stat_s[ub][q][m];
+                const float m2 = stat_m[ub][(it0 + q) % HM_NACC][m], s2 = stat_s[ub][(it0 + q) % HM_NACC][m];
                 const float mn = fmaxf(mm, m2);
                 if (mn != -INFINITY) {
                     ss = ss * hm_ex2((mm - mn) * HM_LOG2E) + s2 * hm_ex2((m2 - mn) * HM_LOG2E);
@@ -329,35 +402,26 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
                 ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = (nt - 1 - j) * HM_KEYS;
-#pragma unroll 1
+                uint32_t va[32], vb[32];
+                tmem_ld_32x32(t_base, va);
+#pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), v);
-                    tmem_ld_wait();
-                    if (c == 3) {
+                    uint32_t (&cur)[32] = (c & 1) ? vb : va;
+                    hm_ld_wait(cur);
+                    if (c < 3) {
+                        tmem_ld_32x32(t_base + (uint32_t)((c + 1) * 32), (c & 1) ? va : vb);
+                    } else {
                         fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[grp]);
                     }
                     const int kb = key0 + c * 32;
                     if (!row_ok || kb >= g.Q) continue;
-                    const int nvalid = n_keys - kb;
                     uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float lo, hi;
-                        hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), lo, hi);
-                        lo = hm_ex2(fmaf(lo, HM_LOG2E, -shift));
-                        hi = hm_ex2(fmaf(hi, HM_LOG2E, -shift));
-                        if (nvalid < 32) {
-                            if (2 * i >= nvalid) lo = 0.0f;
-                            if (2 * i + 1 >= nvalid) hi = 0.0f;
-                        }
-                        pk[i] = hm_pack2<T>(lo, hi);
-                    }
+                    hm_prob32<T>(cur, n_keys - kb, shift, pk);
                     if (wide && kb + 32 <= g.Q) {
-                        hm_st_v8(yrow + kb, pk);
-                        hm_st_v8(yrow + kb + 16, pk + 8);
+                        hm_st_v8(yrow + kb, pk, pol_out);
+                        hm_st_v8(yrow + kb + 16, pk + 8, pol_out);
                     } else {
                         uint4* dst = reinterpret_cast<uint4*>(yrow + kb);
 #pragma unroll
