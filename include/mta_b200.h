@@ -225,7 +225,9 @@ void mta_reset_launch_count(void);
  * 3 tcgen05 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core, 2 tcgen05 tensor-core; key "fused"
  * -> 0 auto (mta_fused_fwd: Q K^T inside the first conv's kernel, the first head mix and the softmax as one kernel;
  * mta_conv_attn_fwd: one kernel), 1 strictly one kernel per stage, 2 the conv attention as three launches over score
- * planes (needs the workspace), 3 Q K^T and the first conv as two kernels.  Returns 0, or 1 for an unknown key/value. */
+ * planes (needs the workspace), 3 Q K^T and the first conv as two kernels; key "mix_softmax" (the head mix + softmax
+ * kernel) -> 0 auto (tcgen05 where it applies: 16-bit activations and weights of one dtype, 8/16/32/64/128 heads),
+ * 1 the mma.sync kernel, 2 tcgen05 or an error.  Returns 0, or 1 for an unknown key/value. */
 int mta_set_variant(const char* key, int value);
 
 #ifdef __cplusplus

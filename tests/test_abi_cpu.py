@@ -67,7 +67,7 @@ def test_workspace_size_formula():
     assert L.mta_conv_attn_workspace_bytes(2, 4, 512, 128, 6, 11, 0, 1, 1) == 2 * 2 * 4 * 512 * 512 * 2      # not causal
     assert L.mta_conv_attn_workspace_bytes(2, 4, 512, 128, 6, 19, 1, 1, 1) == 2 * 2 * 4 * 512 * 512 * 2      # 19 taps wide
     assert L.mta_workspace_bytes(2, 4, 64, 32, 6, 11, 3, 3, 32, 70, 0) == 0
-    assert L.mta_set_variant(b"nope", 1) == 1 and L.mta_set_variant(b"conv2d", 0) == 0
+    assert L.mta_set_variant(b"nope", 1) == 1 and L.mta_set_variant(b"conv2d", 0) == 0 and L.mta_set_variant(b"mix_softmax", 0) == 0
 
 
 def test_ops_refuse_cpu_tensors():
