@@ -109,13 +109,16 @@ int make_tensor_map_3d_mode(CUtensorMap* out, const void* base, uint64_t planes,
     cuuint64_t dims[3] = {cols, rows, planes};
     cuuint64_t strides[2] = {row_pitch_elems * 2, plane_pitch_elems * 2};
     MTA_REQUIRE(box_cols <= 256 && box_rows <= 256 && box_planes >= 1 && box_planes <= 256 && (box_cols * 2) % 16 == 0 && (!swizzle128 || box_cols == 64) &&
-                    (swizzle_bytes != 32 || box_cols == 16) && (swizzle_bytes == 0 || swizzle_bytes == 32 || swizzle_bytes == 128),
+                    (swizzle_bytes != 32 || box_cols == 16) && (swizzle_bytes != 64 || box_cols == 32) &&
+                    (swizzle_bytes == 0 || swizzle_bytes == 32 || swizzle_bytes == 64 || swizzle_bytes == 128),
                 "tensor map: box %u x %u with a %d-byte swizzle is not supported", box_cols, box_rows, swizzle_bytes);
     cuuint32_t box[3] = {box_cols, box_rows, box_planes};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE),
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                               : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                      : (swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE)),
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {

@@ -780,11 +780,10 @@ int head_mix_softmax_launch(const void* x, PlaneView xv, const void* Wm, int w_d
     const bool tc05_able = head_mix_softmax_tc05_supported(x, xv, y, yv, C, Q, 1, dtype, w_dtype);
     MTA_REQUIRE(want != 2 || tc05_able,
                 "head_mix_softmax: the tcgen05 variant needs 16-bit activations and weights of one dtype and 8, 16, 32, 64 or 128 heads");
-    // Measured on B200 (bf16, the same 1.07e9 scores): the tcgen05 kernel takes 0.41 to 0.77 of the mma.sync kernel's time
-    // with 8 or 16 heads (B8 H16 S4096: 1.46 against 2.05 ms with the upper triangle written) and 1.12 to 1.19 of it with
-    // 32 heads (B4 H32 S4096, B1 H32 S8192), so 32 heads stay on the mma.sync kernel, which does not take more than 32.
-    const bool mma_able = mix_softmax_mma_ok(x, xv, y, yv, C, Q, 1, dtype);
-    if (tc05_able && (want == 2 || (want == 0 && (C <= 16 || !mma_able))))
+    // Measured on B200 (bf16, upper triangle written): the tcgen05 kernel takes 0.40 to 0.73 of the mma.sync kernel's time
+    // at every shape tried (B8 H16 S4096: 1.39 against 2.05 ms; B4 H32 S4096: 1.40 against 2.21; B1 H32 S8192: 1.48 against
+    // 2.21; B32 H16 S512: 0.16 against 0.39), so it runs wherever it applies.
+    if (tc05_able && want != 1)
         return head_mix_softmax_tc05_launch(x, xv, Wm, y, yv, N, C, Q, row_begin, row_end, write_upper, dtype, st);
     MTA_REQUIRE(mix_softmax_mma_ok(x, xv, y, yv, C, Q, 1, dtype),
                 "head_mix_softmax: needs a 16-bit dtype, C <= 32, Q %% 8 == 0, 16-byte aligned rows and x != y");

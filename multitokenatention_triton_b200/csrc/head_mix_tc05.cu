@@ -4,8 +4,8 @@
 // mta_attention_triton.py:76-79, triton_linear_head.py:76-139).
 //
 // The mix of R = 128 / C consecutive query rows is ONE matrix product per tile of 128 keys:
-//   D[(r,o)][key] = sum over (h,r') of A[(r,o)][(h,r')] * B[(h,r')][key],
-//   A = the weight repeated on the diagonal blocks (A[(r,o)][(h,r')] = Wm[o,h] when r = r', else 0), built once per CTA,
+//   D[(o,r)][key] = sum over (h,r') of A[(o,r)][(h,r')] * B[(h,r')][key],
+//   A = the weight spread over diagonal blocks (A[(o,r)][(h,r')] = Wm[o,h] when r = r', else 0), built once per CTA,
 //   B = the R rows of all C input planes as they lie in memory (keys contiguous: an MN-major operand), one TMA box of
 //       64 keys x R rows x C planes per half tile.
 // A block-diagonal A wastes R-1 of R multiplications, which the tensor pipe has to spare, and it puts a whole (row, head)
@@ -16,7 +16,8 @@
 //   pass 1  tiles 0 .. diagonal: MMA -> TMEM -> round to the 16-bit dtype (the reference's rounding point) -> running
 //           (maximum, sum of exponentials) per thread; nothing is written;
 //   pass 2  the same tiles from the diagonal back to 0 (the input comes from L2: a unit's rows are at most 1 MB):
-//           MMA again -> round -> 2^(x log2 e - shift) -> 16-bit -> global memory, every thread its own row.
+//           MMA again -> round -> 2^(x log2 e - shift) -> 16-bit -> a staging buffer per softmax group -> one TMA store
+//           per 32 keys x 128 rows (a box of 32 keys x R rows x C planes, the mirror image of the input box).
 // Recomputing the mix costs tensor time that is free here; in exchange the logits never exist in memory.
 //
 // Warps: 0 TMA producer (ring of HM_NSTAGE tiles of 32 KB), 1-2 MMA issuers on alternate tiles (an issuer also zeroes
@@ -39,7 +40,9 @@ constexpr int HM_A_BYTES = 2 * HM_BOX_BYTES;         // the 128 x 128 weight ope
 constexpr int HM_NSTAGE = 4;
 constexpr int HM_NACC = 4;                           // accumulators = softmax groups
 constexpr int HM_SOFTMAX_THREADS = HM_NACC * 128;
-constexpr bool HM_LOAD_HINTS = true, HM_STORE_HINTS = true;   // L2 eviction policies on the TMA loads / the output stores
+constexpr int HM_OUT_BYTES = 128 * 64;                // a group's output staging: 128 rows x 32 keys
+
+constexpr bool HM_LOAD_HINTS = true;                 // L2 eviction policies on the TMA loads
 constexpr int HM_ISSUERS = 2;                        // MMA-issuing warps 1..HM_ISSUERS
 // A barrier's consecutive phases must be awaited by ONE thread: a waiter that looks for the phase after next while the
 // next one is still incomplete reads the parity of the phase before as "done" (try_wait tells two phases apart, no more).
@@ -86,18 +89,6 @@ __device__ __forceinline__ float hm_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-// One 32-byte store: a full sector per thread (every thread writes its own row, so nothing coalesces across a warp).
-__device__ __forceinline__ void hm_st_v8(void* p, const uint32_t* w, uint64_t policy) {
-    if (HM_STORE_HINTS)
-        asm volatile("st.global.L2::cache_hint.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8}, %9;" ::"l"(p), "r"(w[0]), "r"(w[1]),
-                     "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "l"(policy)
-                     : "memory");
-    else
-        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
-                     "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
-                     : "memory");
 }
 
 // tcgen05.wait::ld that also names the 32 registers of a pending load as in-out operands: nothing that uses them can be
@@ -185,8 +176,8 @@ __device__ __forceinline__ int hm_tiles(const HmGeom& g, int p0) {
 
 template <typename T>
 __global__ void __launch_bounds__(HM_THREADS, 1)
-head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __restrict__ Wm, T* __restrict__ y, PlaneView yv,
-                             HmGeom g, int* err_flag) {
+head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my, const T* __restrict__ Wm,
+                             T* __restrict__ y, PlaneView yv, HmGeom g, int* err_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t full_bar[HM_NSTAGE], empty_bar[HM_NSTAGE], acc_full[HM_NACC], acc_empty[HM_NACC];
@@ -195,6 +186,7 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
     __shared__ float stat_m[2][HM_NACC][128], stat_s[2][HM_NACC][128];   // [unit parity][group][lane]
     uint8_t* a_base = smem;
     uint8_t* stage_base = smem + HM_A_BYTES;
+    uint8_t* out_base = stage_base + HM_NSTAGE * HM_STAGE_BYTES;      // HM_NACC staging buffers of HM_OUT_BYTES
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int C = g.C, R = g.R;
 
@@ -214,17 +206,19 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
             }
             fence_mbar_init();
             prefetch_tensormap(&mx);
+            prefetch_tensormap(&my);
         }
         __syncwarp();
         tmem_alloc(&tmem_slot, 512);
     }
     // The weight operand, K-major with the 128-byte swizzle: element (m, k) of K block k / 64 at byte
-    // m * 128 + (((k % 64) / 8) ^ (m % 8)) * 16 + (k % 8) * 2; m = r * C + o, k = h * R + r.
+    // m * 128 + (((k % 64) / 8) ^ (m % 8)) * 16 + (k % 8) * 2; m = o * R + r (the order of the output box's lines),
+    // k = h * R + r (the order of the input box's lines).
     for (int i = tid; i < HM_A_BYTES / 16; i += HM_THREADS) reinterpret_cast<uint4*>(a_base)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
     for (int i = tid; i < 128 * C; i += HM_THREADS) {
         const int m = i / C, h = i % C;
-        const int r = m / C, o = m % C;
+        const int r = m % R, o = m / R;
         const int k = h * R + r, kk = k & 63;
         *reinterpret_cast<T*>(a_base + (k >> 6) * HM_BOX_BYTES + m * 128 + (((kk >> 3) ^ (m & 7)) << 4) + (kk & 7) * 2) = Wm[o * C + h];
     }
@@ -334,11 +328,10 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
     } else if (warp >= HM_FIRST_SOFTMAX_WARP) {
         const int sw = warp - HM_FIRST_SOFTMAX_WARP, grp = sw >> 2, quarter = warp & 3;   // a warp reads the TMEM lanes of its index modulo 4
         const int m = quarter * 32 + lane;
-        const int r = m / C, o = m % C;
+        const int r = m % R, o = m / R;
         const uint32_t t_base = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(grp * HM_KEYS);
-        // rows start on 32-byte boundaries: the 32-byte stores apply
-        const bool wide = (reinterpret_cast<uintptr_t>(y) & 31u) == 0 && yv.width % 16 == 0 && yv.plane_stride % 16 == 0;
-        const uint64_t pol_out = l2_policy_evict_first();   // the output streams through L2: it must not displace the unit's input
+        uint8_t* out_buf = out_base + grp * HM_OUT_BYTES;
+        const int gt = (sw & 3) * 32 + lane;                 // thread index within the group; thread 0 issues the group's stores
         int it = 0;
         int ub = 0;
         bool ok = true;
@@ -346,13 +339,13 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
             const int p = p0 + r;
             const bool row_ok = p < g.row_end;
             const int n_keys = min(p + 1, g.Q);
-            T* yrow = y + yv.at((long)n * C + o, row_ok ? p : p0, 0);
+            const int unit_keys = min(min(p0 + R, g.row_end), g.Q);   // keys that some row of the unit may see
             // ---- pass 1: statistics over this group's tiles ----
             float m_run = -INFINITY, s_run = 0.0f;
-            for (int j = 0; j < nt && ok; ++j) {
+            for (int j = 0; j < nt; ++j) {                         // no early exit after a wait gave up (see below)
                 const int t = it + j;
                 if (t % HM_NACC != grp) continue;
-                ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
+                if (ok) ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = j * HM_KEYS;
                 // the load of the next 32 columns is in flight while these are consumed
@@ -396,10 +389,10 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
             // p = 2^(x log2 e - shift): the division by the sum is folded into the exponent
             const float shift = fmaf(mm, HM_LOG2E, log2f(ss));
             // ---- pass 2: the tiles again, from the diagonal down ----
-            for (int j = 0; j < nt && ok; ++j) {
+            for (int j = 0; j < nt; ++j) {                         // no early exit after a wait gave up (see below)
                 const int t = it + j;
                 if (t % HM_NACC != grp) continue;
-                ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
+                if (ok) ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = (nt - 1 - j) * HM_KEYS;
                 uint32_t va[32], vb[32];
@@ -415,18 +408,26 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[grp]);
                     }
+                    // The 32 keys x 128 rows of the group go out as ONE TMA store (a box of 32 keys x R rows x C planes; rows past
+                    // row_end and keys past Q are clipped by the map): every thread puts its 64 bytes into the group's staging
+                    // buffer (line m, 16-byte pieces swizzled as the 64-byte TMA swizzle expects, which also spreads a warp's
+                    // stores over all banks).  Per-thread stores to global memory, one row each, were the slowest part of pass 2.
+                    // The conditions are the same for every thread of the group: they all meet at the two barriers.
                     const int kb = key0 + c * 32;
-                    if (!row_ok || kb >= g.Q) continue;
+                    if (kb >= g.Q || (kb >= unit_keys && !g.write_upper)) continue;
                     uint32_t pk[16];
                     hm_prob32<T>(cur, n_keys - kb, shift, pk);
-                    if (wide && kb + 32 <= g.Q) {
-                        hm_st_v8(yrow + kb, pk, pol_out);
-                        hm_st_v8(yrow + kb + 16, pk + 8, pol_out);
-                    } else {
-                        uint4* dst = reinterpret_cast<uint4*>(yrow + kb);
+                    if (gt == 0) bulk_wait_read();                   // the previous store of this buffer has read it
+                    named_barrier(2 + grp, 128);
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4)
-                            if (kb + q4 * 8 < g.Q) dst[q4] = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        *reinterpret_cast<uint4*>(out_buf + m * 64 + ((q4 ^ ((m >> 1) & 3)) << 4)) =
+                            make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    fence_proxy_async();
+                    named_barrier(2 + grp, 128);
+                    if (gt == 0) {
+                        tma_store_3d(&my, out_buf, kb, p0 - yv.row0, n * C);
+                        bulk_commit();
                     }
                 }
             }
@@ -440,16 +441,17 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const T* __
                     for (int k = nt * HM_KEYS + lane * 8; k < g.Q; k += 256) *reinterpret_cast<uint4*>(y + off + k) = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
-            // no early exit after a wait gave up: every softmax warp must meet the others at every unit's barrier
+            // no early exit after a wait gave up: every softmax warp must meet the others at every barrier of every unit
         }
     }
 #undef HM_FOR_UNITS
+    if (warp >= HM_FIRST_SOFTMAX_WARP && ((warp - HM_FIRST_SOFTMAX_WARP) & 3) == 0 && lane == 0) bulk_wait_all();
     fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
-constexpr size_t HM_SMEM_BYTES = 1024 + HM_A_BYTES + (size_t)HM_NSTAGE * HM_STAGE_BYTES;
+constexpr size_t HM_SMEM_BYTES = 1024 + HM_A_BYTES + (size_t)HM_NSTAGE * HM_STAGE_BYTES + (size_t)HM_NACC * HM_OUT_BYTES;
 
 template <typename T>
 int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q, int row_begin, int row_end,
@@ -466,6 +468,10 @@ int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv
     if ((rc = make_tensor_map_3d_mode(&mx, x, (uint64_t)N * C, (uint64_t)(row_end - xv.row0), (uint64_t)Q, (uint64_t)xv.width,
                                       (uint64_t)xv.plane_stride, 64, (uint32_t)g.R, 128, (uint32_t)C)))
         return rc;
+    CUtensorMap my;
+    if ((rc = make_tensor_map_3d_mode(&my, y, (uint64_t)N * C, (uint64_t)(row_end - yv.row0), (uint64_t)Q, (uint64_t)yv.width,
+                                      (uint64_t)yv.plane_stride, 32, (uint32_t)g.R, 64, (uint32_t)C)))
+        return rc;
     int* flag = nullptr;
     if ((rc = wait_flag_ptr(&flag))) return rc;
     int dev = 0, sms = 0;
@@ -473,7 +479,7 @@ int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv
     MTA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_softmax_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HM_SMEM_BYTES));
     const unsigned grid = (unsigned)std::min<long>(g.units, sms);
-    head_mix_softmax_tc05_kernel<T><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, static_cast<const T*>(Wm), static_cast<T*>(y), yv, g, flag);
+    head_mix_softmax_tc05_kernel<T><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, my, static_cast<const T*>(Wm), static_cast<T*>(y), yv, g, flag);
     MTA_LAUNCH_OK("head_mix_softmax_tc05_kernel");
     return MTA_OK;
 }

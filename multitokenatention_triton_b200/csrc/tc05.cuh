@@ -264,7 +264,7 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // 3-D map over [planes][rows][cols] of 16-bit elements (cols contiguous, row pitch `row_pitch_elems`, plane pitch
 // `plane_pitch_elems`), box = box_cols x box_rows x 1 plane, with the 128-byte swizzle (box_cols must be 64) or
 // without a swizzle; out-of-bounds reads give zero.
-// As make_tensor_map_3d with the swizzle given in bytes: 0 (none), 32 (box of 16 columns) or 128 (box of 64 columns),
+// As make_tensor_map_3d with the swizzle given in bytes: 0 (none), 32 (box of 16 columns), 64 (32 columns) or 128 (64 columns),
 // and a box that spans box_planes consecutive planes (it lands in shared memory as [plane][row][column]).
 int make_tensor_map_3d_mode(CUtensorMap* out, const void* base, uint64_t planes, uint64_t rows, uint64_t cols,
                             uint64_t row_pitch_elems, uint64_t plane_pitch_elems, uint32_t box_cols, uint32_t box_rows,
