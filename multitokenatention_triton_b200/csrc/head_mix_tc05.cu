@@ -42,7 +42,6 @@ constexpr int HM_NACC = 4;                           // accumulators = softmax g
 constexpr int HM_SOFTMAX_THREADS = HM_NACC * 128;
 constexpr int HM_OUT_BYTES = 128 * 64;                // a group's output staging: 128 rows x 32 keys
 
-constexpr bool HM_LOAD_HINTS = true;                 // L2 eviction policies on the TMA loads
 constexpr int HM_ISSUERS = 2;                        // MMA-issuing warps 1..HM_ISSUERS
 // A barrier's consecutive phases must be awaited by ONE thread: a waiter that looks for the phase after next while the
 // next one is still incomplete reads the parity of the phase before as "done" (try_wait tells two phases apart, no more).
@@ -246,7 +245,7 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
     if (warp == 0) {
         if (lane == 0) {
             // Pass 1 asks L2 to keep what it reads (pass 2 reads it again within the unit), pass 2 reads it for the last time.
-            const uint64_t pol_keep = HM_LOAD_HINTS ? l2_policy_evict_last() : 0, pol_drop = HM_LOAD_HINTS ? l2_policy_evict_first() : 0;
+            const uint64_t pol_keep = l2_policy_evict_last(), pol_drop = l2_policy_evict_first();
             int it = 0;
             bool ok = true;
             HM_FOR_UNITS
@@ -257,14 +256,9 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
                     if (use > 0 && !(ok = mbar_wait(&empty_bar[st], (uint32_t)((use - 1) & 1), err_flag))) break;
                     uint8_t* dst = stage_base + st * HM_STAGE_BYTES;
                     mbar_expect_tx(&full_bar[st], HM_STAGE_BYTES);
-                    if (HM_LOAD_HINTS) {
-                        const uint64_t pol = j < nt ? pol_keep : pol_drop;
-                        tma_load_3d_hint(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C, pol);
-                        tma_load_3d_hint(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C, pol);
-                    } else {
-                        tma_load_3d(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C);
-                        tma_load_3d(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C);
-                    }
+                    const uint64_t pol = j < nt ? pol_keep : pol_drop;
+                    tma_load_3d_hint(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C, pol);
+                    tma_load_3d_hint(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C, pol);
                 }
                 if (!ok) break;
             }

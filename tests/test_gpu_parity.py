@@ -337,6 +337,25 @@ def test_scores_computed_inside_the_first_conv_change_no_bit(name):
     assert torch.equal(part[:, :, 9:wl.S - 2], folded[:, :, 9:wl.S - 2])
 
 
+@pytest.mark.parametrize("H,dtype", [(16, torch.bfloat16), (32, torch.float16), (8, torch.bfloat16)])
+def test_row_range_over_many_key_tiles_changes_no_bit(H, dtype):
+    """Rows long enough for eight key tiles of the head mix + softmax kernel, whose partial row statistics come from four
+    groups of warps: a row range that starts at an odd row (other row groups, other tile counts before each unit) must
+    reproduce the full run bit for bit, and two full runs must agree."""
+    wl = MTAWorkload("rowrange", 2, H, 1000, 64, 6, 11, 3, 3, dtype, seed=300 + H, random_post_conv=True)
+    inp = make_mta_inputs(wl)
+    args = [inp[k].to(DEV) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    full = ops.mta_fused_fwd(*args, True)
+    assert torch.equal(full, ops.mta_fused_fwd(*args, True))
+    for r0, r1 in ((37, 911), (512, 1000), (0, 130)):
+        part = torch.zeros_like(full)
+        ops.mta_fused_fwd(*args, True, rows=(r0, r1), out=part)
+        assert torch.equal(part[:, :, r0:r1], full[:, :, r0:r1]), f"rows [{r0},{r1})"
+    _lib.device_status()
+    a = [npf(inp[k]) for k in ("q", "k", "v", "w1", "W1", "w2", "W2")]
+    assert_parity(npf(full), orc.mta_fwd(*a, True, orc.ROUND_NONE), dtype, f"H{H} S1000 vs oracle")
+
+
 @pytest.mark.parametrize("H,S,D,cq,ck,dtype", [(128, 72, 32, 3, 5, torch.float16), (4, 160, 64, 77, 77, torch.float16),
                                               (64, 96, 64, 6, 11, torch.bfloat16), (2, 200, 128, 21, 21, torch.float32)])
 def test_mta_forward_published_shape_limits(H, S, D, cq, ck, dtype):
