@@ -221,7 +221,7 @@ long mta_launch_count(void);
 void mta_reset_launch_count(void);
 
 /* Selects implementation variants for A/B measurement (process-wide, atomically updated, read on every launch):
- * key "head_linear" -> 0 auto, 1 CUDA-core, 2 tensor-core; key "conv2d" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core,
+ * key "head_linear" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core, 3 tcgen05 tensor-core; key "conv2d" -> 0 auto, 1 CUDA-core, 2 mma.sync tensor-core,
  * 3 tcgen05 tensor-core; key "gemm" (the two contractions) -> 0 auto, 1 CUDA-core, 2 tcgen05 tensor-core; key "fused"
  * -> 0 auto (mta_fused_fwd: Q K^T inside the first conv's kernel, the first head mix and the softmax as one kernel;
  * mta_conv_attn_fwd: one kernel), 1 strictly one kernel per stage, 2 the conv attention as three launches over score

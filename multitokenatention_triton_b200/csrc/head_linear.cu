@@ -807,9 +807,18 @@ int head_linear_launch(const void* x, PlaneView xv, const void* Wm, int w_dtype,
     if (N == 0 || row_end <= row_begin || Q == 0) return MTA_OK;
     MTA_REQUIRE(C >= 1 && C <= 128, "head_linear: C = %d heads is outside the supported range 1..128", C);
     MTA_REQUIRE(N <= 65535 && row_end - row_begin <= 65535, "head_linear: N or the row count exceeds 65535");
+    // variant "head_linear": 0 auto, 1 CUDA cores, 2 mma.sync, 3 tcgen05
     const int want = variant("head_linear");
     const bool mma_able = dtype != MTA_F32 && C <= 32 && Q % 8 == 0 && vector_ok(x, xv) && vector_ok(y, yv);
-    MTA_REQUIRE(want != 2 || mma_able, "head_linear: the tensor-core variant needs a 16-bit dtype, C <= 32, Q %% 8 == 0 and 16-byte aligned rows");
+    const bool tc05_able = head_linear_tc05_supported(x, xv, y, yv, C, Q, dtype, w_dtype);
+    MTA_REQUIRE(want != 2 || mma_able, "head_linear: the mma.sync variant needs a 16-bit dtype, C <= 32, Q %% 8 == 0 and 16-byte aligned rows");
+    MTA_REQUIRE(want != 3 || tc05_able,
+                "head_linear: the tcgen05 variant needs 16-bit activations and weights of one dtype, 8, 16, 32, 64 or 128 heads and x != y");
+    // Measured on B200 (bf16, causal, upper triangle written): up to 32 heads the mma.sync kernel already runs at 78 to 87 %
+    // of the copy bandwidth and the tcgen05 kernel takes 0.95 to 1.16 of its time (B4 H16 S2048: 0.173 against 0.160 ms),
+    // so tcgen05 is the default only for 64 and 128 heads, which the mma.sync kernel does not take.
+    if (tc05_able && (want == 3 || (want == 0 && !mma_able)))
+        return head_linear_tc05_launch(x, xv, Wm, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, dtype, st);
     const bool use_mma = mma_able && want != 1;
     if (dtype == MTA_F32)
         return dispatch_simt<float>(x, xv, Wm, w_dtype, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st);

@@ -162,21 +162,38 @@ __device__ __forceinline__ void hm_prob32(const uint32_t (&v)[32], int nvalid, f
     }
 }
 
+// The plain head mix on 32 keys: the products rounded to T, two per word; keys from nvalid on become `fill`.
+template <typename T>
+__device__ __forceinline__ void hm_plain32(const uint32_t (&v)[32], int nvalid, float fill, uint32_t (&pk)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
+        if (nvalid < 32) {
+            if (2 * i >= nvalid) lo = fill;
+            if (2 * i + 1 >= nvalid) hi = fill;
+        }
+        pk[i] = hm_pack2<T>(lo, hi);
+    }
+}
+
 struct HmGeom {
-    int N, C, R, Q, row_begin, row_end, groups, write_upper, x_row0;
+    int N, C, R, Q, row_begin, row_end, groups, write_upper, x_row0, causal, wt;
+    float fill;          // value of the entries above the diagonal (plain head mix; the softmax writes 0 there)
     long units;
 };
 
 // Key tiles that the rows of the group starting at p0 reach.
 __device__ __forceinline__ int hm_tiles(const HmGeom& g, int p0) {
     const int p_last = min(p0 + g.R, g.row_end) - 1;
-    return (min(p_last + 1, g.Q) + HM_KEYS - 1) / HM_KEYS;
+    return ((g.causal ? min(p_last + 1, g.Q) : g.Q) + HM_KEYS - 1) / HM_KEYS;
 }
 
-template <typename T>
+// SOFTMAX: the two-pass kernel described at the top.  Otherwise the plain head mix (linear_head_kernel_forward,
+// triton_linear_head.py:76-139): one pass, the rounded products go out as they are, `fill` above the diagonal.
+template <typename T, bool SOFTMAX>
 __global__ void __launch_bounds__(HM_THREADS, 1)
-head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my, const T* __restrict__ Wm,
-                             T* __restrict__ y, PlaneView yv, HmGeom g, int* err_flag) {
+head_mix_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my, const T* __restrict__ Wm,
+                     int y_row0, HmGeom g, int* err_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t full_bar[HM_NSTAGE], empty_bar[HM_NSTAGE], acc_full[HM_NACC], acc_empty[HM_NACC];
@@ -186,6 +203,8 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
     uint8_t* a_base = smem;
     uint8_t* stage_base = smem + HM_A_BYTES;
     uint8_t* out_base = stage_base + HM_NSTAGE * HM_STAGE_BYTES;      // HM_NACC staging buffers of HM_OUT_BYTES
+    uint8_t* fill_base = out_base + HM_NACC * HM_OUT_BYTES;           // one more, holding `fill` (0 for the softmax) everywhere
+    constexpr int PASSES = SOFTMAX ? 2 : 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int C = g.C, R = g.R;
 
@@ -214,12 +233,16 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
     // m * 128 + (((k % 64) / 8) ^ (m % 8)) * 16 + (k % 8) * 2; m = o * R + r (the order of the output box's lines),
     // k = h * R + r (the order of the input box's lines).
     for (int i = tid; i < HM_A_BYTES / 16; i += HM_THREADS) reinterpret_cast<uint4*>(a_base)[i] = make_uint4(0u, 0u, 0u, 0u);
+    {
+        const uint32_t f2 = SOFTMAX ? 0u : hm_pack2<T>(g.fill, g.fill);
+        for (int i = tid; i < HM_OUT_BYTES / 16; i += HM_THREADS) reinterpret_cast<uint4*>(fill_base)[i] = make_uint4(f2, f2, f2, f2);
+    }
     __syncthreads();
     for (int i = tid; i < 128 * C; i += HM_THREADS) {
         const int m = i / C, h = i % C;
         const int r = m % R, o = m / R;
         const int k = h * R + r, kk = k & 63;
-        *reinterpret_cast<T*>(a_base + (k >> 6) * HM_BOX_BYTES + m * 128 + (((kk >> 3) ^ (m & 7)) << 4) + (kk & 7) * 2) = Wm[o * C + h];
+        *reinterpret_cast<T*>(a_base + (k >> 6) * HM_BOX_BYTES + m * 128 + (((kk >> 3) ^ (m & 7)) << 4) + (kk & 7) * 2) = g.wt ? Wm[h * C + o] : Wm[o * C + h];
     }
     fence_proxy_async();
     fence_before_sync();
@@ -249,14 +272,14 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
             int it = 0;
             bool ok = true;
             HM_FOR_UNITS
-                for (int j = 0; j < 2 * nt && ok; ++j, ++it) {
+                for (int j = 0; j < PASSES * nt && ok; ++j, ++it) {
                     const int kt = j < nt ? j : 2 * nt - 1 - j;
                     const int st = it % HM_NSTAGE;
                     const int use = it / HM_NSTAGE;
                     if (use > 0 && !(ok = mbar_wait(&empty_bar[st], (uint32_t)((use - 1) & 1), err_flag))) break;
                     uint8_t* dst = stage_base + st * HM_STAGE_BYTES;
                     mbar_expect_tx(&full_bar[st], HM_STAGE_BYTES);
-                    const uint64_t pol = j < nt ? pol_keep : pol_drop;
+                    const uint64_t pol = (SOFTMAX && j < nt) ? pol_keep : pol_drop;
                     tma_load_3d_hint(dst, &mx, &full_bar[st], kt * HM_KEYS, p0 - g.x_row0, n * C, pol);
                     tma_load_3d_hint(dst + HM_BOX_BYTES, &mx, &full_bar[st], kt * HM_KEYS + 64, p0 - g.x_row0, n * C, pol);
                 }
@@ -271,7 +294,7 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
         int it = 0;
         bool ok = true;
         HM_FOR_UNITS
-            for (int j = 0; j < 2 * nt && ok; ++j, ++it) {
+            for (int j = 0; j < PASSES * nt && ok; ++j, ++it) {
                 if (it % HM_ISSUERS != issuer) continue;
                 const int kt = j < nt ? j : 2 * nt - 1 - j;
                 const int st = it % HM_NSTAGE, ab = it % HM_NACC;
@@ -282,7 +305,7 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
                 // through the zeros of A.  Only keys p0+1 .. p0+R-1 matter (later keys are masked for every row of the
                 // group): in line l = h * R + r', which holds row p0 + r', the keys p0+r'+1 .. p0+R-1 become 0.
                 const int key0 = kt * HM_KEYS;
-                if (p0 + R - 1 >= key0 && p0 + 1 < key0 + HM_KEYS) {
+                if (g.causal && p0 + R - 1 >= key0 && p0 + 1 < key0 + HM_KEYS) {
                     // the 16-byte pieces (8 keys) that hold keys p0+1 .. p0+R-1 of this tile: one when p0 is a multiple of 8
                     const int c_lo = max(p0 + 1 - key0, 0) >> 3, c_hi = min(p0 + R - 1 - key0, HM_KEYS - 1) >> 3;
                     for (int l = lane; l < 128; l += 32) {
@@ -322,7 +345,7 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
     } else if (warp >= HM_FIRST_SOFTMAX_WARP) {
         const int sw = warp - HM_FIRST_SOFTMAX_WARP, grp = sw >> 2, quarter = warp & 3;   // a warp reads the TMEM lanes of its index modulo 4
         const int m = quarter * 32 + lane;
-        const int r = m % R, o = m / R;
+        const int r = m % R;
         const uint32_t t_base = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(grp * HM_KEYS);
         uint8_t* out_buf = out_base + grp * HM_OUT_BYTES;
         const int gt = (sw & 3) * 32 + lane;                 // thread index within the group; thread 0 issues the group's stores
@@ -331,9 +354,10 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
         bool ok = true;
         HM_FOR_UNITS
             const int p = p0 + r;
-            const bool row_ok = p < g.row_end;
-            const int n_keys = min(p + 1, g.Q);
-            const int unit_keys = min(min(p0 + R, g.row_end), g.Q);   // keys that some row of the unit may see
+            const int n_keys = g.causal ? min(p + 1, g.Q) : g.Q;
+            const int unit_keys = g.causal ? min(min(p0 + R, g.row_end), g.Q) : g.Q;   // keys that some row of the unit may see
+            float shift = 0.0f;
+            if constexpr (SOFTMAX) {
             // ---- pass 1: statistics over this group's tiles ----
             float m_run = -INFINITY, s_run = 0.0f;
             for (int j = 0; j < nt; ++j) {                         // no early exit after a wait gave up (see below)
@@ -381,14 +405,15 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
             }
             ub ^= 1;
             // p = 2^(x log2 e - shift): the division by the sum is folded into the exponent
-            const float shift = fmaf(mm, HM_LOG2E, log2f(ss));
-            // ---- pass 2: the tiles again, from the diagonal down ----
+            shift = fmaf(mm, HM_LOG2E, log2f(ss));
+            }
+            // ---- the output pass: for the softmax the tiles again, from the diagonal down ----
             for (int j = 0; j < nt; ++j) {                         // no early exit after a wait gave up (see below)
                 const int t = it + j;
                 if (t % HM_NACC != grp) continue;
                 if (ok) ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
-                const int key0 = (nt - 1 - j) * HM_KEYS;
+                const int key0 = (SOFTMAX ? nt - 1 - j : j) * HM_KEYS;
                 uint32_t va[32], vb[32];
                 tmem_ld_32x32(t_base, va);
 #pragma unroll
@@ -410,7 +435,8 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
                     const int kb = key0 + c * 32;
                     if (kb >= g.Q || (kb >= unit_keys && !g.write_upper)) continue;
                     uint32_t pk[16];
-                    hm_prob32<T>(cur, n_keys - kb, shift, pk);
+                    if constexpr (SOFTMAX) hm_prob32<T>(cur, n_keys - kb, shift, pk);
+                    else hm_plain32<T>(cur, n_keys - kb, g.fill, pk);
                     if (gt == 0) bulk_wait_read();                   // the previous store of this buffer has read it
                     named_barrier(2 + grp, 128);
 #pragma unroll
@@ -420,19 +446,18 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
                     fence_proxy_async();
                     named_barrier(2 + grp, 128);
                     if (gt == 0) {
-                        tma_store_3d(&my, out_buf, kb, p0 - yv.row0, n * C);
+                        tma_store_3d(&my, out_buf, kb, p0 - y_row0, n * C);
                         bulk_commit();
                     }
                 }
             }
             it += nt;
-            if (g.write_upper && grp == 0 && nt * HM_KEYS < g.Q) {
-                // probabilities past the last tile are exactly 0: a warp fills its 32 rows one after the other
-                const long row_off = yv.at((long)n * C + o, row_ok ? p : p0, 0);
-                for (int i = 0; i < 32; ++i) {
-                    const long off = __shfl_sync(0xffffffffu, row_off, i);
-                    if (!__shfl_sync(0xffffffffu, row_ok ? 1 : 0, i)) continue;
-                    for (int k = nt * HM_KEYS + lane * 8; k < g.Q; k += 256) *reinterpret_cast<uint4*>(y + off + k) = make_uint4(0u, 0u, 0u, 0u);
+            if (g.write_upper && gt == 0) {
+                // Everything past the unit's last tile is `fill` (0 for the softmax): boxes of the constant buffer, the
+                // groups taking turns.  Nobody waits for these stores before the kernel ends.
+                for (int kb = nt * HM_KEYS + grp * 32; kb < g.Q; kb += HM_NACC * 32) {
+                    tma_store_3d(&my, fill_base, kb, p0 - y_row0, n * C);
+                    bulk_commit();
                 }
             }
             // no early exit after a wait gave up: every softmax warp must meet the others at every barrier of every unit
@@ -445,24 +470,27 @@ head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __gri
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
-constexpr size_t HM_SMEM_BYTES = 1024 + HM_A_BYTES + (size_t)HM_NSTAGE * HM_STAGE_BYTES + (size_t)HM_NACC * HM_OUT_BYTES;
+constexpr size_t HM_SMEM_BYTES = 1024 + HM_A_BYTES + (size_t)HM_NSTAGE * HM_STAGE_BYTES + (size_t)(HM_NACC + 1) * HM_OUT_BYTES;
 
-template <typename T>
-int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q, int row_begin, int row_end,
-              bool write_upper, cudaStream_t st) {
+template <typename T, bool SOFTMAX>
+int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q, int causal, float fill,
+              int row_begin, int row_end, bool write_upper, bool wt, cudaStream_t st) {
     HmGeom g{};
     g.N = N; g.C = C; g.R = 128 / C; g.Q = Q; g.row_begin = row_begin; g.row_end = row_end;
     g.groups = (row_end - row_begin + g.R - 1) / g.R;
-    g.write_upper = write_upper ? 1 : 0;
+    g.write_upper = (write_upper && causal) ? 1 : 0;
     g.x_row0 = xv.row0;
+    g.causal = causal ? 1 : 0;
+    g.wt = wt ? 1 : 0;
+    g.fill = fill;
     g.units = (long)N * g.groups;
-    CUtensorMap mx;
+    CUtensorMap mx, my;
     int rc;
-    // rows past row_end read as zero: they are lines of the B operand and must not carry anything into the product
+    // rows past row_end read as zero (they are lines of the B operand and must not carry anything into the product) and
+    // are not written
     if ((rc = make_tensor_map_3d_mode(&mx, x, (uint64_t)N * C, (uint64_t)(row_end - xv.row0), (uint64_t)Q, (uint64_t)xv.width,
                                       (uint64_t)xv.plane_stride, 64, (uint32_t)g.R, 128, (uint32_t)C)))
         return rc;
-    CUtensorMap my;
     if ((rc = make_tensor_map_3d_mode(&my, y, (uint64_t)N * C, (uint64_t)(row_end - yv.row0), (uint64_t)Q, (uint64_t)yv.width,
                                       (uint64_t)yv.plane_stride, 32, (uint32_t)g.R, 64, (uint32_t)C)))
         return rc;
@@ -471,27 +499,44 @@ int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv
     int dev = 0, sms = 0;
     MTA_CUDA_OK(cudaGetDevice(&dev));
     MTA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_softmax_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HM_SMEM_BYTES));
+    MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_tc05_kernel<T, SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HM_SMEM_BYTES));
     const unsigned grid = (unsigned)std::min<long>(g.units, sms);
-    head_mix_softmax_tc05_kernel<T><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, my, static_cast<const T*>(Wm), static_cast<T*>(y), yv, g, flag);
-    MTA_LAUNCH_OK("head_mix_softmax_tc05_kernel");
+    head_mix_tc05_kernel<T, SOFTMAX><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, my, static_cast<const T*>(Wm), yv.row0, g, flag);
+    MTA_LAUNCH_OK(SOFTMAX ? "head_mix_tc05_kernel (softmax)" : "head_mix_tc05_kernel");
     return MTA_OK;
+}
+
+bool hm_tc05_ok(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int dtype, int w_dtype) {
+    const bool pow2 = C >= 8 && C <= 128 && (C & (C - 1)) == 0;
+    return dtype != MTA_F32 && w_dtype == dtype && pow2 && Q % 8 == 0 && x != y && aligned16(x) && aligned16(y) &&
+           xv.width % 8 == 0 && xv.plane_stride % 8 == 0 && yv.width % 8 == 0 && yv.plane_stride % 8 == 0;
 }
 
 }  // namespace
 
 bool head_mix_softmax_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int causal, int dtype,
                                      int w_dtype) {
-    const bool pow2 = C >= 8 && C <= 128 && (C & (C - 1)) == 0;
-    return causal && dtype != MTA_F32 && w_dtype == dtype && pow2 && Q % 8 == 0 && x != y && aligned16(x) && aligned16(y) &&
-           xv.width % 8 == 0 && xv.plane_stride % 8 == 0 && yv.width % 8 == 0 && yv.plane_stride % 8 == 0;
+    return causal && hm_tc05_ok(x, xv, y, yv, C, Q, dtype, w_dtype);
 }
 
 int head_mix_softmax_tc05_launch(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q,
                                  int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st) {
     if (N == 0 || row_end <= row_begin || Q == 0) return MTA_OK;
-    if (dtype == MTA_BF16) return launch_hm<__nv_bfloat16>(x, xv, Wm, y, yv, N, C, Q, row_begin, row_end, write_upper, st);
-    return launch_hm<__half>(x, xv, Wm, y, yv, N, C, Q, row_begin, row_end, write_upper, st);
+    if (dtype == MTA_BF16)
+        return launch_hm<__nv_bfloat16, true>(x, xv, Wm, y, yv, N, C, Q, 1, 0.0f, row_begin, row_end, write_upper, false, st);
+    return launch_hm<__half, true>(x, xv, Wm, y, yv, N, C, Q, 1, 0.0f, row_begin, row_end, write_upper, false, st);
+}
+
+bool head_linear_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int dtype, int w_dtype) {
+    return hm_tc05_ok(x, xv, y, yv, C, Q, dtype, w_dtype);
+}
+
+int head_linear_tc05_launch(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q, int causal,
+                            float fill, int row_begin, int row_end, bool write_upper, bool wt, int dtype, cudaStream_t st) {
+    if (N == 0 || row_end <= row_begin || Q == 0) return MTA_OK;
+    if (dtype == MTA_BF16)
+        return launch_hm<__nv_bfloat16, false>(x, xv, Wm, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st);
+    return launch_hm<__half, false>(x, xv, Wm, y, yv, N, C, Q, causal, fill, row_begin, row_end, write_upper, wt, st);
 }
 
 }  // namespace mta

@@ -51,6 +51,12 @@ bool head_mix_softmax_tc05_supported(const void* x, PlaneView xv, const void* y,
 int head_mix_softmax_tc05_launch(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q,
                                  int row_begin, int row_end, bool write_upper, int dtype, cudaStream_t st);
 
+// The plain head mix on the same kernel (one pass): y = Wm x over the head axis (Wm read transposed when `wt`), `fill`
+// above the diagonal when causal (written up to the end of the diagonal's key tile, and up to Q when `write_upper`).
+bool head_linear_tc05_supported(const void* x, PlaneView xv, const void* y, PlaneView yv, int C, int Q, int dtype, int w_dtype);
+int head_linear_tc05_launch(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv, int N, int C, int Q, int causal,
+                            float fill, int row_begin, int row_end, bool write_upper, bool wt, int dtype, cudaStream_t st);
+
 // Causal row softmax of pre_scale * x; rows [row_begin,row_end).
 int softmax_launch(const void* x, PlaneView xv, void* y, PlaneView yv, long planes, int P, int Q, int causal,
                    int row_begin, int row_end, bool write_upper, float pre_scale, int dtype, cudaStream_t st);

@@ -106,13 +106,15 @@ def test_conv2d_rectangular_noncausal():
 
 
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 @pytest.mark.parametrize("name", list(HEAD_CASES))
 def test_head_linear(name, variant, golden):
     N, C, S, dtype, seed, causal, fill = HEAD_CASES[name]
     mma_able = dtype != torch.float32 and C <= 32 and S % 8 == 0
     if variant == 2 and not mma_able:
         pytest.skip("tensor-core variant needs a 16-bit dtype, C <= 32 and S % 8 == 0")
+    if variant == 3 and not (dtype != torch.float32 and C in (8, 16, 32, 64, 128) and S % 8 == 0):
+        pytest.skip("the tcgen05 variant needs a 16-bit dtype, 8, 16, 32, 64 or 128 heads and S % 8 == 0")
     inp = make_head_linear_inputs(N, C, S, dtype, seed)
     m = TritonLinearHead(C, causal=causal, output_value=fill).to(DEV).to(dtype)
     _lib.set_variant("head_linear", variant)
@@ -141,6 +143,41 @@ def test_head_linear_head_counts(C, dtype):
     y = ops.head_linear_fwd(inp["x"].to(DEV), W32.to(DEV), True, float("-inf"))
     ref = orc.head_linear(npf(inp["x"]), npf(W32), True, float("-inf"), ROUND[dtype])
     one_stage_close(npf(y), ref, dtype, f"C={C}")
+
+
+@pytest.mark.parametrize("variant", [2, 3])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("C,S,causal,fill", [(16, 520, True, 0.0), (16, 1304, True, float("-inf")), (8, 264, True, 0.0),
+                                             (32, 1032, True, 0.0), (64, 200, True, float("-inf")), (128, 136, True, 0.0),
+                                             (16, 264, False, 0.0), (32, 136, False, 0.0)])
+def test_head_linear_16bit_weights(C, S, causal, fill, dtype, variant):
+    """Weights in the activations' dtype, rows of several key tiles: the tcgen05 kernel (3) and the mma.sync kernel (2)
+    against the oracle; NaN above the diagonal of the input must change nothing; the part above the diagonal is `fill`."""
+    if variant == 2 and C > 32:
+        pytest.skip("the mma.sync kernel takes up to 32 heads")
+    g = torch.Generator().manual_seed(2900 + C + S)
+    x = torch.randn(2, C, S, S, generator=g).to(dtype)
+    W = (torch.eye(C) + 0.3 * torch.randn(C, C, generator=g)).to(dtype)
+    _lib.set_variant("head_linear", variant)
+    try:
+        _lib.reset_launch_count()
+        y = ops.head_linear_fwd(x.to(DEV), W.to(DEV), causal, fill)
+        assert _lib.launch_count() == 1
+        if causal:
+            xn = x.clone()
+            iu = torch.triu_indices(S, S, 1)
+            xn[..., iu[0], iu[1]] = float("nan")
+            yn = ops.head_linear_fwd(xn.to(DEV), W.to(DEV), causal, fill)
+            assert torch.equal(y, yn)
+    finally:
+        _lib.set_variant("head_linear", 0)
+    _lib.device_status()
+    ref = orc.head_linear(npf(x), npf(W), causal, fill, ROUND[dtype])
+    one_stage_close(npf(y), ref, dtype, f"C={C} S={S} causal={causal}")
+    if causal:
+        iu = np.triu_indices(S, 1)
+        up = npf(y)[..., iu[0], iu[1]]
+        assert np.all(up == fill) if np.isfinite(fill) else np.all(np.isneginf(up))
 
 
 def test_head_linear_ignores_input_above_diagonal():
