@@ -191,9 +191,8 @@ __device__ __forceinline__ int hm_tiles(const HmGeom& g, int p0) {
 // SOFTMAX: the two-pass kernel described at the top.  Otherwise the plain head mix (linear_head_kernel_forward,
 // triton_linear_head.py:76-139): one pass, the rounded products go out as they are, `fill` above the diagonal.
 template <typename T, bool SOFTMAX>
-__global__ void __launch_bounds__(HM_THREADS, 1)
-head_mix_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my, const T* __restrict__ Wm,
-                     int y_row0, HmGeom g, int* err_flag) {
+__device__ __forceinline__ void head_mix_tc05_body(const CUtensorMap& mx, const CUtensorMap& my, const T* __restrict__ Wm, int y_row0,
+                                                   const HmGeom& g, int* err_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t full_bar[HM_NSTAGE], empty_bar[HM_NSTAGE], acc_full[HM_NACC], acc_empty[HM_NACC];
@@ -470,6 +469,19 @@ head_mix_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_consta
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+template <typename T>
+__global__ void __launch_bounds__(HM_THREADS, 1)
+head_mix_softmax_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my, const T* __restrict__ Wm,
+                             int y_row0, HmGeom g, int* err_flag) {
+    head_mix_tc05_body<T, true>(mx, my, Wm, y_row0, g, err_flag);
+}
+template <typename T>
+__global__ void __launch_bounds__(HM_THREADS, 1)
+head_mix_plain_tc05_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap my, const T* __restrict__ Wm,
+                           int y_row0, HmGeom g, int* err_flag) {
+    head_mix_tc05_body<T, false>(mx, my, Wm, y_row0, g, err_flag);
+}
+
 constexpr size_t HM_SMEM_BYTES = 1024 + HM_A_BYTES + (size_t)HM_NSTAGE * HM_STAGE_BYTES + (size_t)(HM_NACC + 1) * HM_OUT_BYTES;
 
 template <typename T, bool SOFTMAX>
@@ -499,10 +511,15 @@ int launch_hm(const void* x, PlaneView xv, const void* Wm, void* y, PlaneView yv
     int dev = 0, sms = 0;
     MTA_CUDA_OK(cudaGetDevice(&dev));
     MTA_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_tc05_kernel<T, SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HM_SMEM_BYTES));
     const unsigned grid = (unsigned)std::min<long>(g.units, sms);
-    head_mix_tc05_kernel<T, SOFTMAX><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, my, static_cast<const T*>(Wm), yv.row0, g, flag);
-    MTA_LAUNCH_OK(SOFTMAX ? "head_mix_tc05_kernel (softmax)" : "head_mix_tc05_kernel");
+    if constexpr (SOFTMAX) {
+        MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_softmax_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HM_SMEM_BYTES));
+        head_mix_softmax_tc05_kernel<T><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, my, static_cast<const T*>(Wm), yv.row0, g, flag);
+    } else {
+        MTA_CUDA_OK(cudaFuncSetAttribute(head_mix_plain_tc05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HM_SMEM_BYTES));
+        head_mix_plain_tc05_kernel<T><<<grid, HM_THREADS, HM_SMEM_BYTES, st>>>(mx, my, static_cast<const T*>(Wm), yv.row0, g, flag);
+    }
+    MTA_LAUNCH_OK(SOFTMAX ? "head_mix_softmax_tc05_kernel" : "head_mix_plain_tc05_kernel");
     return MTA_OK;
 }
 
