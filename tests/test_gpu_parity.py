@@ -180,6 +180,30 @@ def test_head_linear_16bit_weights(C, S, causal, fill, dtype, variant):
         assert np.all(up == fill) if np.isfinite(fill) else np.all(np.isneginf(up))
 
 
+@pytest.mark.parametrize("P,Q,causal", [(200, 136, True), (100, 264, True), (37, 152, False), (300, 64, False)])
+def test_head_linear_rectangular_on_tcgen05(P, Q, causal):
+    """Planes with more rows than keys and the other way round, on the tcgen05 kernels: the plain head mix and, for the
+    causal shapes, head mix + softmax (rows past the last key see every key)."""
+    g = torch.Generator().manual_seed(31 * P + Q)
+    x = (2 * torch.randn(2, 16, P, Q, generator=g)).to(torch.bfloat16)
+    W = (torch.eye(16) + 0.3 * torch.randn(16, 16, generator=g)).to(torch.bfloat16)
+    _lib.set_variant("head_linear", 3)
+    _lib.set_variant("mix_softmax", 2)
+    try:
+        y = ops.head_linear_fwd(x.to(DEV), W.to(DEV), causal, 0.0)
+        ys = ops.head_linear_softmax_fwd(x.to(DEV), W.to(DEV)) if causal else None
+    finally:
+        _lib.set_variant("head_linear", 0)
+        _lib.set_variant("mix_softmax", 0)
+    _lib.device_status()
+    one_stage_close(npf(y), orc.head_linear(npf(x), npf(W), causal, 0.0, orc.ROUND_BF16), torch.bfloat16, f"{P}x{Q}")
+    if causal:
+        mixed = orc.head_linear(npf(x), npf(W), True, float("-inf"), orc.ROUND_BF16)
+        ref = orc.softmax(mixed, True, orc.ROUND_BF16)
+        tol = 2.0 * ULP[torch.bfloat16] * max(1.0, float(np.max(np.abs(mixed[np.isfinite(mixed)]))))
+        assert max_abs(npf(ys), ref) <= tol
+
+
 def test_head_linear_ignores_input_above_diagonal():
     inp = make_head_linear_inputs(1, 16, 128, torch.bfloat16, seed=77)
     x = inp["x"].clone()
