@@ -148,31 +148,36 @@ __device__ __forceinline__ void hm_stats32(const uint32_t (&v)[32], int nvalid, 
 template <typename T>
 __device__ __forceinline__ void hm_prob32(const uint32_t (&v)[32], int nvalid, float shift, uint32_t (&pk)[16]) {
     const float2 l2 = make_float2(HM_LOG2E, HM_LOG2E), ns = make_float2(-shift, -shift);
+    // two copies of the loop: a compiler that turns the masking into selects would spend two of them on every score
+    if (nvalid >= 32) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        float2 f;
-        hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), f.x, f.y);
-        const float2 yv = __ffma2_rn(f, l2, ns);
-        float lo = hm_ex2(yv.x), hi = hm_ex2(yv.y);
-        if (nvalid < 32) {
-            if (2 * i >= nvalid) lo = 0.0f;
-            if (2 * i + 1 >= nvalid) hi = 0.0f;
+        for (int i = 0; i < 16; ++i) {
+            float2 f;
+            hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), f.x, f.y);
+            const float2 yv = __ffma2_rn(f, l2, ns);
+            pk[i] = hm_pack2<T>(hm_ex2(yv.x), hm_ex2(yv.y));
         }
-        pk[i] = hm_pack2<T>(lo, hi);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float2 f;
+            hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), f.x, f.y);
+            const float2 yv = __ffma2_rn(f, l2, ns);
+            pk[i] = hm_pack2<T>(2 * i < nvalid ? hm_ex2(yv.x) : 0.0f, 2 * i + 1 < nvalid ? hm_ex2(yv.y) : 0.0f);
+        }
     }
 }
 
 // The plain head mix on 32 keys: the products rounded to T, two per word; keys from nvalid on become `fill`.
 template <typename T>
 __device__ __forceinline__ void hm_plain32(const uint32_t (&v)[32], int nvalid, float fill, uint32_t (&pk)[16]) {
+    if (nvalid >= 32) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        float lo = __uint_as_float(v[2 * i]), hi = __uint_as_float(v[2 * i + 1]);
-        if (nvalid < 32) {
-            if (2 * i >= nvalid) lo = fill;
-            if (2 * i + 1 >= nvalid) hi = fill;
-        }
-        pk[i] = hm_pack2<T>(lo, hi);
+        for (int i = 0; i < 16; ++i) pk[i] = hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            pk[i] = hm_pack2<T>(2 * i < nvalid ? __uint_as_float(v[2 * i]) : fill, 2 * i + 1 < nvalid ? __uint_as_float(v[2 * i + 1]) : fill);
     }
 }
 
