@@ -90,18 +90,6 @@ __device__ __forceinline__ float hm_ex2(float x) {
     return y;
 }
 
-// tcgen05.wait::ld that also names the 32 registers of a pending load as in-out operands: nothing that uses them can be
-// scheduled before the wait, and a load into the other buffer may be in flight while this buffer is consumed.
-__device__ __forceinline__ void hm_ld_wait(uint32_t (&r)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
-                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
-                   "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
-                   "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-                 :
-                 : "memory");
-}
-
 // Pass 1 on 32 keys of a row: the logits rounded to T, their maximum folded into (m_run, s_run).
 template <typename T>
 __device__ __forceinline__ void hm_stats32(const uint32_t (&v)[32], int nvalid, float& m_run, float& s_run) {
@@ -370,16 +358,12 @@ __device__ __forceinline__ void head_mix_tc05_body(const CUtensorMap& mx, const 
                 if (ok) ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = j * HM_KEYS;
-                // the load of the next 32 columns is in flight while these are consumed
-                uint32_t va[32], vb[32];
-                tmem_ld_32x32(t_base, va);
-#pragma unroll
+                uint32_t cur[32];
+#pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t (&cur)[32] = (c & 1) ? vb : va;
-                    hm_ld_wait(cur);
-                    if (c < 3) {
-                        tmem_ld_32x32(t_base + (uint32_t)((c + 1) * 32), (c & 1) ? va : vb);
-                    } else {
+                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), cur);
+                    tmem_ld_wait();
+                    if (c == 3) {
                         fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[grp]);
@@ -418,15 +402,12 @@ __device__ __forceinline__ void head_mix_tc05_body(const CUtensorMap& mx, const 
                 if (ok) ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = (SOFTMAX ? nt - 1 - j : j) * HM_KEYS;
-                uint32_t va[32], vb[32];
-                tmem_ld_32x32(t_base, va);
-#pragma unroll
+                uint32_t cur[32];
+#pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t (&cur)[32] = (c & 1) ? vb : va;
-                    hm_ld_wait(cur);
-                    if (c < 3) {
-                        tmem_ld_32x32(t_base + (uint32_t)((c + 1) * 32), (c & 1) ? va : vb);
-                    } else {
+                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), cur);
+                    tmem_ld_wait();
+                    if (c == 3) {
                         fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[grp]);
