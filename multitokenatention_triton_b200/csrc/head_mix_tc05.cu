@@ -90,12 +90,35 @@ __device__ __forceinline__ float hm_ex2(float x) {
     return y;
 }
 
+// 32 fp32 columns of this thread's TMEM lane, rounded to T and packed two per word (word i = columns 2i, 2i+1), as ONE
+// asm statement: the 32 loaded values never become C++ variables, only the 16 packed words do.
+template <typename T> __device__ __forceinline__ void hm_ld_round32(uint32_t taddr, uint32_t (&pk)[16]);
+#define HM_LD_ROUND32(CVT)                                                                                              \
+    asm volatile(                                                                                                       \
+        "{\n\t.reg .b32 t<32>;\n\t"                                                                                    \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                       \
+        "{t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, "                                       \
+        "t16, t17, t18, t19, t20, t21, t22, t23, t24, t25, t26, t27, t28, t29, t30, t31}, [%16];\n\t"                   \
+        "tcgen05.wait::ld.sync.aligned;\n\t"                                                                            \
+        CVT " %0, t1, t0;\n\t" CVT " %1, t3, t2;\n\t" CVT " %2, t5, t4;\n\t" CVT " %3, t7, t6;\n\t"                      \
+        CVT " %4, t9, t8;\n\t" CVT " %5, t11, t10;\n\t" CVT " %6, t13, t12;\n\t" CVT " %7, t15, t14;\n\t"                \
+        CVT " %8, t17, t16;\n\t" CVT " %9, t19, t18;\n\t" CVT " %10, t21, t20;\n\t" CVT " %11, t23, t22;\n\t"            \
+        CVT " %12, t25, t24;\n\t" CVT " %13, t27, t26;\n\t" CVT " %14, t29, t28;\n\t" CVT " %15, t31, t30;\n\t}\n"       \
+        : "=r"(pk[0]), "=r"(pk[1]), "=r"(pk[2]), "=r"(pk[3]), "=r"(pk[4]), "=r"(pk[5]), "=r"(pk[6]), "=r"(pk[7]), "=r"(pk[8]), \
+          "=r"(pk[9]), "=r"(pk[10]), "=r"(pk[11]), "=r"(pk[12]), "=r"(pk[13]), "=r"(pk[14]), "=r"(pk[15])                 \
+        : "r"(taddr)                                                                                                    \
+        : "memory")
+template <> __device__ __forceinline__ void hm_ld_round32<__nv_bfloat16>(uint32_t taddr, uint32_t (&pk)[16]) {
+    HM_LD_ROUND32("cvt.rn.bf16x2.f32");
+}
+template <> __device__ __forceinline__ void hm_ld_round32<__half>(uint32_t taddr, uint32_t (&pk)[16]) {
+    HM_LD_ROUND32("cvt.rn.f16x2.f32");
+}
+#undef HM_LD_ROUND32
+
 // Pass 1 on 32 keys of a row: the logits rounded to T, their maximum folded into (m_run, s_run).
 template <typename T>
-__device__ __forceinline__ void hm_stats32(const uint32_t (&v)[32], int nvalid, float& m_run, float& s_run) {
-    uint32_t pk[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) pk[i] = hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+__device__ __forceinline__ void hm_stats32(const uint32_t (&pk)[16], int nvalid, float& m_run, float& s_run) {
     float2 f[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) hm_unpack2<T>(pk[i], f[i].x, f[i].y);
@@ -134,14 +157,14 @@ __device__ __forceinline__ void hm_stats32(const uint32_t (&v)[32], int nvalid, 
 
 // Pass 2 on 32 keys: the logits rounded to T -> probabilities in T, two per word; keys from nvalid on become 0.
 template <typename T>
-__device__ __forceinline__ void hm_prob32(const uint32_t (&v)[32], int nvalid, float shift, uint32_t (&pk)[16]) {
+__device__ __forceinline__ void hm_prob32(const uint32_t (&in)[16], int nvalid, float shift, uint32_t (&pk)[16]) {
     const float2 l2 = make_float2(HM_LOG2E, HM_LOG2E), ns = make_float2(-shift, -shift);
     // two copies of the loop: a compiler that turns the masking into selects would spend two of them on every score
     if (nvalid >= 32) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             float2 f;
-            hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), f.x, f.y);
+            hm_unpack2<T>(in[i], f.x, f.y);
             const float2 yv = __ffma2_rn(f, l2, ns);
             pk[i] = hm_pack2<T>(hm_ex2(yv.x), hm_ex2(yv.y));
         }
@@ -149,7 +172,7 @@ __device__ __forceinline__ void hm_prob32(const uint32_t (&v)[32], int nvalid, f
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             float2 f;
-            hm_unpack2<T>(hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), f.x, f.y);
+            hm_unpack2<T>(in[i], f.x, f.y);
             const float2 yv = __ffma2_rn(f, l2, ns);
             pk[i] = hm_pack2<T>(2 * i < nvalid ? hm_ex2(yv.x) : 0.0f, 2 * i + 1 < nvalid ? hm_ex2(yv.y) : 0.0f);
         }
@@ -158,14 +181,15 @@ __device__ __forceinline__ void hm_prob32(const uint32_t (&v)[32], int nvalid, f
 
 // The plain head mix on 32 keys: the products rounded to T, two per word; keys from nvalid on become `fill`.
 template <typename T>
-__device__ __forceinline__ void hm_plain32(const uint32_t (&v)[32], int nvalid, float fill, uint32_t (&pk)[16]) {
+__device__ __forceinline__ void hm_plain32(const uint32_t (&in)[16], int nvalid, float fill, uint32_t (&pk)[16]) {
     if (nvalid >= 32) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) pk[i] = hm_pack2<T>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+        for (int i = 0; i < 16; ++i) pk[i] = in[i];
     } else {
+        const uint32_t f2 = hm_pack2<T>(fill, fill);
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-            pk[i] = hm_pack2<T>(2 * i < nvalid ? __uint_as_float(v[2 * i]) : fill, 2 * i + 1 < nvalid ? __uint_as_float(v[2 * i + 1]) : fill);
+            pk[i] = (2 * i < nvalid ? in[i] & 0x0000ffffu : f2 & 0x0000ffffu) | (2 * i + 1 < nvalid ? in[i] & 0xffff0000u : f2 & 0xffff0000u);
     }
 }
 
@@ -358,11 +382,10 @@ __device__ __forceinline__ void head_mix_tc05_body(const CUtensorMap& mx, const 
                 if (ok) ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = j * HM_KEYS;
-                uint32_t cur[32];
+                uint32_t cur[16];
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
-                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), cur);
-                    tmem_ld_wait();
+                    hm_ld_round32<T>(t_base + (uint32_t)(c * 32), cur);
                     if (c == 3) {
                         fence_before_sync();
                         __syncwarp();
@@ -402,11 +425,10 @@ __device__ __forceinline__ void head_mix_tc05_body(const CUtensorMap& mx, const 
                 if (ok) ok = mbar_wait_spin(&acc_full[grp], (uint32_t)((t / HM_NACC) & 1), err_flag);
                 fence_after_sync();
                 const int key0 = (SOFTMAX ? nt - 1 - j : j) * HM_KEYS;
-                uint32_t cur[32];
+                uint32_t cur[16];
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
-                    tmem_ld_32x32(t_base + (uint32_t)(c * 32), cur);
-                    tmem_ld_wait();
+                    hm_ld_round32<T>(t_base + (uint32_t)(c * 32), cur);
                     if (c == 3) {
                         fence_before_sync();
                         __syncwarp();
